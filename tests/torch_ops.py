@@ -54,11 +54,63 @@ class TorchOps:
     def prepare(self, dtype, sampling=True):
         pass
 
-    def check_attention_sizes(self, n_heads, n_kv_heads, head_dim, dtype):
-        assert n_heads % n_kv_heads == 0 and head_dim % 2 == 0
+    def check_attention_sizes(self, n_heads, n_kv_heads, head_dim, dtype, v_head_dim=None):
+        assert n_heads % n_kv_heads == 0 and head_dim > 0
 
-    def embed(self, token_ids, table):
-        return table[token_ids.long()].float()
+    def embed(self, token_ids, table, scale=1.0, positions=None, position_table=None):
+        h = table[token_ids.long()].float() * np.float32(scale)
+        if position_table is not None:
+            h = h + position_table[positions.long()].float()
+        return h
+
+    def stream_rows(self, h, dtype):
+        return h if dtype == torch.float32 else h.to(dtype)
+
+    def norm_add(self, h, delta, weight, eps, out_dtype):
+        """h += delta / sqrt(mean(delta^2) + eps) * weight (in place, float32); the new rows in out_dtype."""
+        if isinstance(delta, PendingProduct):
+            delta = delta.take(self)
+        d = delta.float().sum(0) if delta.dim() == 3 else delta.float()
+        h += d * torch.rsqrt(d.pow(2).mean(-1, keepdim=True) + eps) * weight
+        return self.stream_rows(h, out_dtype)
+
+    def glu(self, gate_up, out_dtype=None, *, limit, alpha, up_offset):
+        out_dtype = out_dtype or gate_up.dtype
+        if gate_up.dim() == 3:
+            gate_up = gate_up.float().sum(0)
+        hidden = gate_up.shape[1] // 2
+        g = gate_up[:, :hidden].float().clamp(max=limit)
+        u = gate_up[:, hidden:].float().clamp(min=-limit, max=limit)
+        return (g * torch.sigmoid(alpha * g) * (u + up_offset)).to(out_dtype)
+
+    def linear_glu(self, x, w_gate_up, *, limit, alpha, up_offset):
+        return self.glu(self.linear(x, w_gate_up, partials_ok=True), out_dtype=x.dtype, limit=limit, alpha=alpha,
+                        up_offset=up_offset)
+
+    def project_and_store(self, proj, *, n_q, n_k, n_v, n_extra, bias, q_norm, k_norm, eps, k_pages, v_pages,
+                          slot_mapping, page_size, out_dtype):
+        """A row of proj is [q | k | v | extra].  Bias added, q and k each normalised over their whole
+        width (where a weight is given), k and v written to their pages, sigmoid of the extra columns."""
+        x = proj.float().sum(0) if proj.dim() == 3 else proj.float()
+        assert x.shape[1] == n_q + n_k + n_v + n_extra
+        if bias is not None:
+            x = x + bias
+        q, k, v, e = x.split([n_q, n_k, n_v, n_extra], dim=1)
+        if q_norm is not None:
+            q = q * torch.rsqrt(q.pow(2).mean(-1, keepdim=True) + eps) * q_norm
+        if k_norm is not None and n_k:
+            k = k * torch.rsqrt(k.pow(2).mean(-1, keepdim=True) + eps) * k_norm
+        if k_pages is not None and n_k:
+            sm = slot_mapping.long()
+            page, slot = sm // page_size, sm % page_size
+            k_pages[page, :, slot] = k.reshape(k.shape[0], k_pages.shape[1], k_pages.shape[3]).to(k_pages.dtype)
+            if v_pages is not None and n_v:
+                v_pages[page, :, slot] = v.reshape(v.shape[0], v_pages.shape[1], v_pages.shape[3]).to(v_pages.dtype)
+        return q.to(out_dtype).contiguous(), (torch.sigmoid(e).to(out_dtype).contiguous() if n_extra else None)
+
+    def head_linear(self, x, w):
+        """x [T, H, K] against w [H, N, K]: out[t, h] = w[h] @ x[t, h]."""
+        return torch.einsum("thk,hnk->thn", x.float(), w.float()).to(x.dtype).contiguous()
 
     def rmsnorm(self, h, delta, weight, eps, out_dtype, rows=None, deferred=False):
         if isinstance(delta, PendingProduct):
@@ -157,10 +209,15 @@ class TorchOps:
         return q
 
     def paged_attention(self, q, k_pages, v_pages, block_table, q_start, kv_len, *, n_seqs, max_q_len,
-                        max_kv_len, scale, window, page_size, allow_split=True, impl="auto", n_tokens=None, out=None):
+                        max_kv_len, scale, window, page_size, allow_split=True, impl="auto", n_tokens=None, out=None,
+                        keep_first=0, distance_bias=None, distance_buckets=None, gate=None):
         T, H, hd = q.shape
         KV = k_pages.shape[1]
         group = H // KV
+        if keep_first or distance_bias is not None or gate is not None or v_pages.shape[3] != hd:
+            assert out is None and n_tokens is None
+            return self._attention_general(q, k_pages, v_pages, block_table, q_start, kv_len, n_seqs, scale, window,
+                                           page_size, keep_first, distance_bias, distance_buckets, gate)
         # the same contract as the kernels' front end: the step's bounds cover its requests and fit the table
         assert block_table.shape[1] * page_size >= max_kv_len, "block_table is too narrow for max_kv_len"
         assert int(kv_len[:n_seqs].max()) <= max_kv_len and n_seqs <= block_table.shape[0]
@@ -186,6 +243,41 @@ class TorchOps:
                 s = (qq[:, h] @ k[:, h // group].T) * scale
                 s = s.masked_fill(hidden, float("-inf"))
                 out[qs[b]:qs[b + 1], h] = (torch.softmax(s, -1) @ v[:, h // group]).to(q.dtype)
+        return out
+
+    def _attention_general(self, q, k_pages, v_pages, block_table, q_start, kv_len, n_seqs, scale, window, page_size,
+                           keep_first, distance_bias, distance_buckets, gate):
+        """Everything the general kernel can do, key by visible key: kept first tokens behind a
+        window, a bias by bucketed distance, values of another size, an output gate per head
+        ([T, H]) or per element ([T, H * dv])."""
+        T, H, hd = q.shape
+        KV, dv = k_pages.shape[1], v_pages.shape[3]
+        group = H // KV
+        out = torch.zeros((T, H, dv), dtype=q.dtype, device=q.device)
+        qs, kl = q_start.tolist(), kv_len.tolist()
+        for b in range(n_seqs):
+            ql, L = qs[b + 1] - qs[b], kl[b]
+            qpos = torch.arange(L - ql, L, device=q.device)
+            lo = max(0, (L - ql) - window + 1) if window else 0
+            pos = torch.cat([torch.arange(0, min(keep_first, lo), device=q.device), torch.arange(lo, L, device=q.device)])
+            pages = block_table[b].long()[pos // page_size]
+            assert (pages >= 0).all(), "attention would read a page that was given back"
+            k = k_pages[pages, :, pos % page_size].float()
+            v = v_pages[pages, :, pos % page_size].float()
+            qq = q[qs[b]:qs[b + 1]].float()
+            dist = qpos[:, None] - pos[None, :]
+            hidden = dist < 0
+            if window:
+                hidden = hidden | ((dist >= window) & (pos[None, :] >= keep_first))
+            for h in range(H):
+                s = (qq[:, h] @ k[:, h // group].T) * scale
+                if distance_bias is not None:
+                    s = s + distance_bias[distance_buckets[dist.clamp(min=0)].long(), h]
+                o = torch.softmax(s.masked_fill(hidden, float("-inf")), -1) @ v[:, h // group]
+                if gate is not None:
+                    g = gate[qs[b]:qs[b + 1]].float()
+                    o = o * (g[:, h:h + 1] if gate.shape[1] == H else g.view(ql, H, dv)[:, h])
+                out[qs[b]:qs[b + 1], h] = o.to(q.dtype)
         return out
 
     def sample(self, logits, temperature=None, top_k=None, row_keys=None):

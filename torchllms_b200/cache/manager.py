@@ -9,7 +9,9 @@ handles that are never used twice (:271-281) and an invariant checker
 (:797-843).  Different from it: growth is all-or-nothing over a whole batch;
 runs of layers are sorted into *groups* by what they need (all keys, or a
 window of them), each group with pages and block tables of its own, a window
-group giving pages back once the window has passed them; and every live
+group giving pages back once the window has passed them (all but the pages of
+the first tokens, where the need says that those are read for ever); values may
+have another size than keys, or not be stored at all; and every live
 request also owns a dense *slot* that indexes fixed-size state rows and the
 engine's static per-request buffers.
 
@@ -97,7 +99,7 @@ class RunCacheView:
     """What one run of a mixer sees of the cache during a step."""
 
     k_pages: Optional[torch.Tensor]      # [pages, kv_heads, page_size, head_dim]
-    v_pages: Optional[torch.Tensor]
+    v_pages: Optional[torch.Tensor]      # [pages, kv_heads, page_size, value_dim]; None where only keys are stored
     block_table: Optional[torch.Tensor]  # [n_seqs, max_blocks] int32, FREED where no page
     slot_mapping: Optional[torch.Tensor]  # [n_tokens] int32: page * page_size + offset
     page_size: int
@@ -116,13 +118,15 @@ class CacheGroup:
         self.runs = list(runs)
         self.page_size = page_size
         self.allocator = PageAllocator(n_pages)
-        shape = (len(runs), n_pages, need.n_kv_heads, page_size, need.head_dim)
-        self.k_pages = torch.zeros(shape, dtype=dtype, device=device)
-        self.v_pages = torch.zeros(shape, dtype=dtype, device=device)
+        shape = (len(runs), n_pages, need.n_kv_heads, page_size)
+        self.k_pages = torch.zeros(shape + (need.head_dim,), dtype=dtype, device=device)
+        self.v_pages = torch.zeros(shape + (need.value_dim,), dtype=dtype, device=device) if need.value_dim else None
         self.run_index = {run: i for i, run in enumerate(self.runs)}
+        # blocks that hold the first tokens a window keeps: never given back while the request lives
+        self.kept_blocks = -(-need.keep_first // page_size) if need.kind == "window" else 0
 
     def bytes(self) -> int:
-        return 2 * self.k_pages.numel() * self.k_pages.element_size()
+        return sum(t.numel() * t.element_size() for t in (self.k_pages, self.v_pages) if t is not None)
 
 
 class CacheManager:
@@ -152,17 +156,26 @@ class CacheManager:
         self.groups: List[CacheGroup] = []
         self._group_of_run: List[Optional[int]] = [None] * self.n_runs
         self._owner_of_run: List[Optional[int]] = [None] * self.n_runs
-        by_need: Dict[CacheNeed, List[int]] = {}
+        # what a run's pages must keep: what the run itself reads, and what every run that reads
+        # its cache (through a mask of its own) reads
+        keeps: Dict[int, CacheNeed] = {i: need for i, (need, _s, cache_of) in enumerate(run_needs)
+                                       if cache_of is None and need is not None}
         for i, (need, _state, cache_of) in enumerate(run_needs):
-            if cache_of is not None:
-                continue
-            if need is not None:
-                by_need.setdefault(need, []).append(i)
+            if cache_of is not None and need is not None:
+                if cache_of not in keeps:
+                    raise ValueError(f"run {i} reads the cache of run {cache_of}, which has none")
+                try:
+                    keeps[cache_of] = keeps[cache_of].covering(need)
+                except ValueError:
+                    raise ValueError(f"run {i} cannot read run {cache_of}'s cache: head layout differs") from None
+        by_need: Dict[CacheNeed, List[int]] = {}
+        for i, need in keeps.items():
+            by_need.setdefault(need, []).append(i)
         for need, runs in by_need.items():
             n_pages = full_pages
             if need.kind == "window":
                 step = max_step_tokens if max_step_tokens is not None else self.max_len
-                per_req = -(-(need.window + step) // self.page_size) + 1
+                per_req = -(-(need.window + step) // self.page_size) + 1 + -(-need.keep_first // self.page_size)
                 n_pages = min(full_pages, self.max_num_seqs * per_req)
             g = CacheGroup(len(self.groups), need, runs, n_pages, self.page_size, dtype, self.device)
             self.groups.append(g)
@@ -173,9 +186,6 @@ class CacheManager:
             if cache_of is not None:
                 if self._group_of_run[cache_of] is None:
                     raise ValueError(f"run {i} reads the cache of run {cache_of}, which has none")
-                donor = run_needs[cache_of][0]
-                if need is not None and (need.n_kv_heads, need.head_dim) != (donor.n_kv_heads, donor.head_dim):
-                    raise ValueError(f"run {i} cannot read run {cache_of}'s cache: head layout differs")
                 self._group_of_run[i] = self._group_of_run[cache_of]
                 self._owner_of_run[i] = cache_of
 
@@ -319,8 +329,9 @@ class CacheManager:
     def pass_window(self, handle: int) -> int:
         """After a step: give back the pages of window groups that no later query can see.
 
-        A query at position ``p`` of a window ``w`` reads keys ``p - w + 1 .. p``;
-        the next query sits at ``length``.  Returns how many pages were freed."""
+        A query at position ``p`` of a window ``w`` reads keys ``p - w + 1 .. p`` (and the
+        first ``keep_first`` keys, whose blocks stay); the next query sits at ``length``.
+        Returns how many pages were freed."""
         req = self._req(handle)
         freed = 0
         for gi, g in enumerate(self.groups):
@@ -328,7 +339,7 @@ class CacheManager:
                 continue
             first_needed = req.length - g.need.window + 1
             last_dead_block = first_needed // self.page_size if first_needed > 0 else 0
-            for b in range(req.first_block[gi], min(last_dead_block, len(req.blocks[gi]))):
+            for b in range(max(req.first_block[gi], g.kept_blocks), min(last_dead_block, len(req.blocks[gi]))):
                 p = req.blocks[gi][b]
                 if p != FREED:
                     g.allocator.release(p)
@@ -345,7 +356,7 @@ class CacheManager:
             raise CacheError(f"request {handle}: cannot truncate {req.length} tokens to {new_length}")
         keep = -(-new_length // self.page_size)
         for gi, g in enumerate(self.groups):       # check every group before touching any
-            if g.need.kind == "window" and req.first_block[gi] > 0:
+            if g.need.kind == "window" and req.first_block[gi] > g.kept_blocks:
                 first_needed = new_length - g.need.window + 1
                 if first_needed < req.first_block[gi] * self.page_size:
                     raise CacheError(
@@ -383,7 +394,7 @@ class CacheManager:
         g = self.groups[gi]
         owner = self._owner_of_run[run]
         i = g.run_index[owner]
-        return RunCacheView(g.k_pages[i], g.v_pages[i], block_tables[gi], slot_mappings[gi],
+        return RunCacheView(g.k_pages[i], None if g.v_pages is None else g.v_pages[i], block_tables[gi], slot_mappings[gi],
                             self.page_size, owner == run, state, g.need.window)
 
     # --------------------------------------------------------------- invariants
@@ -399,10 +410,10 @@ class CacheManager:
                         f"group {gi} request {req.handle}: {len(blocks)} blocks for {req.length} tokens")
                 for b, p in enumerate(blocks):
                     if p == FREED:
-                        if g.need.kind != "window" or b >= req.first_block[gi]:
+                        if g.need.kind != "window" or b >= req.first_block[gi] or b < g.kept_blocks:
                             raise AssertionError(f"group {gi} request {req.handle}: block {b} has no page")
                         continue
-                    if b < req.first_block[gi]:
+                    if g.kept_blocks <= b < req.first_block[gi]:
                         raise AssertionError(f"group {gi} request {req.handle}: block {b} kept below the window")
                     held[p] = held.get(p, 0) + 1
                 row = self._tables[gi][req.slot]

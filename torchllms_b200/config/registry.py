@@ -66,6 +66,8 @@ def architecture_of(raw: Mapping[str, Any], source: str) -> Architecture:
         # Transformer is the Llama decoder unless a flag says otherwise.
         return get_architecture("LlamaForCausalLM")
     archs = raw.get("architectures")
+    if archs is None and isinstance(raw.get("architecture"), str):
+        archs = [raw["architecture"]]            # some families write the one name as a string
     if not isinstance(archs, (list, tuple)) or not archs or not isinstance(archs[0], str):
         raise ConfigError(f"{source}: missing required key 'architectures' (a list with one name)")
     return get_architecture(archs[0])

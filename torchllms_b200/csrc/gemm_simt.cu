@@ -6,6 +6,10 @@
 // 64 x 64 output tile per CTA, K walked 16 at a time through shared memory, 4 x 4 outputs per
 // thread; every edge is guarded, so M, N and K may be anything.  The K loop order is the same
 // for every row, so a row's result does not depend on which other rows share the launch.
+//
+// The batched form takes one product per blockIdx.z with strides of its own for the rows of A and
+// C and between the batches: a head's slice of [tokens, heads, K] rows against that head's own
+// [N, K] matrix, written into its slice of [tokens, heads, N].
 #include "common.cuh"
 
 namespace {
@@ -14,7 +18,12 @@ constexpr int BM = 64, BN = 64, BK = 16, PAD = 4, NT = 256;
 
 template <typename T, typename TO>
 __global__ void __launch_bounds__(NT) gemm_simt_kernel(const T* __restrict__ A, const T* __restrict__ W,
-                                                       TO* __restrict__ C, int M, int N, int K) {
+                                                       TO* __restrict__ C, int M, int N, int K,
+                                                       long long lda, long long ldc, long long a_batch,
+                                                       long long w_batch, long long c_batch) {
+    A += blockIdx.z * a_batch;
+    W += blockIdx.z * w_batch;
+    C += blockIdx.z * c_batch;
     __shared__ float As[BK][BM + PAD];
     __shared__ float Ws[BK][BN + PAD];
     const int tid = threadIdx.x;
@@ -34,7 +43,7 @@ __global__ void __launch_bounds__(NT) gemm_simt_kernel(const T* __restrict__ A, 
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int gk = k0 + lk + e;
-                As[lk + e][lrow] = (gm < M && gk < K) ? to_float(A[(size_t)gm * K + gk]) : 0.f;
+                As[lk + e][lrow] = (gm < M && gk < K) ? to_float(A[(size_t)gm * lda + gk]) : 0.f;
                 Ws[lk + e][lrow] = (gn < N && gk < K) ? to_float(W[(size_t)gn * K + gk]) : 0.f;
             }
         }
@@ -59,16 +68,18 @@ __global__ void __launch_bounds__(NT) gemm_simt_kernel(const T* __restrict__ A, 
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int gn = n0 + tx * 4 + j;
-            if (gn < N) C[(size_t)gm * N + gn] = from_float<TO>(acc[i][j]);
+            if (gn < N) C[(size_t)gm * ldc + gn] = from_float<TO>(acc[i][j]);
         }
     }
 }
 
 template <typename T, typename TO>
-int launch(const void* A, const void* W, void* C, int M, int N, int K, cudaStream_t s) {
-    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-    if (grid.y > 65535) return TL_BAD_SIZE;
-    gemm_simt_kernel<T, TO><<<grid, NT, 0, s>>>((const T*)A, (const T*)W, (TO*)C, M, N, K);
+int launch(const void* A, const void* W, void* C, int M, int N, int K, cudaStream_t s, int batches = 1,
+           long long lda = -1, long long ldc = -1, long long a_batch = 0, long long w_batch = 0, long long c_batch = 0) {
+    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, batches);
+    if (grid.y > 65535 || batches > 65535) return TL_BAD_SIZE;
+    gemm_simt_kernel<T, TO><<<grid, NT, 0, s>>>((const T*)A, (const T*)W, (TO*)C, M, N, K, lda < 0 ? K : lda,
+                                                ldc < 0 ? N : ldc, a_batch, w_batch, c_batch);
     TL_LAUNCH_CHECK();
     return TL_OK;
 }
@@ -83,5 +94,20 @@ extern "C" int tl_gemm_simt(const void* A, const void* W, void* C, int in_dtype,
     if (in_dtype == TL_F32 && out_dtype == TL_F32) return launch<float, float>(A, W, C, M, N, K, s);
     if (in_dtype == TL_BF16 && out_dtype == TL_BF16) return launch<__nv_bfloat16, __nv_bfloat16>(A, W, C, M, N, K, s);
     if (in_dtype == TL_BF16 && out_dtype == TL_F32) return launch<__nv_bfloat16, float>(A, W, C, M, N, K, s);
+    return TL_BAD_DTYPE;
+}
+
+// One product per head: x [tokens, heads, K] against w [heads, N, K] gives out [tokens, heads, N],
+// out[t, h, :] = w[h] x[t, h, :]; x, w and out have one dtype.
+extern "C" int tl_head_linear(const void* x, const void* w, void* out, int dtype, int n_tokens, int n_heads,
+                              int N, int K, void* stream) {
+    if (n_tokens <= 0 || n_heads <= 0 || N <= 0) return TL_OK;
+    if (K <= 0) return TL_BAD_SIZE;
+    cudaStream_t s = (cudaStream_t)stream;
+    const long long lda = (long long)n_heads * K, ldc = (long long)n_heads * N;
+    if (dtype == TL_F32)
+        return launch<float, float>(x, w, out, n_tokens, N, K, s, n_heads, lda, ldc, K, (long long)N * K, N);
+    if (dtype == TL_BF16)
+        return launch<__nv_bfloat16, __nv_bfloat16>(x, w, out, n_tokens, N, K, s, n_heads, lda, ldc, K, (long long)N * K, N);
     return TL_BAD_DTYPE;
 }

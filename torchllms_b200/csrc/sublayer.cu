@@ -1,0 +1,318 @@
+// What stands between the matrix products of a layer whose norms sit on the sublayers' outputs:
+//
+// embed_positions:  h[t] = table[id[t]] * scale + positions[p[t]]       (float32 stream; optionally
+//                   the same rows in bfloat16 for the first product)
+// stream_rows:      the float32 stream in bfloat16
+// norm_add:         d = sum of delta's planes;  h[t] += d / sqrt(mean(d^2) + eps) * w   (float32),
+//                   and the new h[t] in bfloat16 for the sublayer that reads the stream next
+// glu_clamped:      g = min(gate, limit), u = clamp(up, -limit, limit);
+//                   y = g * sigmoid(alpha * g) * (u + up_offset)        (float32 arithmetic)
+// project_store:    a row of a stacked projection [q | k | v | extra]: bias added, q and k each
+//                   RMS-normed over their *whole* width (where they have a weight), k and v written
+//                   into their pages, q and sigmoid(extra) returned
+//
+// Every sum, norm and activation is float32; rows are rounded once, where they leave.
+#include "common.cuh"
+
+namespace {
+
+__device__ __forceinline__ float block_sum(float v, float* part) {
+    // part: 33 floats of shared memory
+    v = warp_sum(v);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = (blockDim.x + 31) >> 5;
+    __syncthreads();            // part may still be read from an earlier call
+    if (lane == 0) part[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < n_warps ? part[lane] : 0.f;
+        t = warp_sum(t);
+        if (lane == 0) part[32] = t;
+    }
+    __syncthreads();
+    return part[32];
+}
+
+template <typename T>
+__global__ void embed_positions_kernel(const int* __restrict__ ids, const int* __restrict__ positions,
+                                       const T* __restrict__ table, const T* __restrict__ pos_table, float scale,
+                                       float* __restrict__ out, __nv_bfloat16* __restrict__ rows_out, int dim,
+                                       int vocab, int n_positions) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const int t = blockIdx.x;
+    int id = ids[t];
+    (void)TL_CHECK(id >= 0 && id < vocab, TL_DBG_TOKEN_ID);
+    id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);   // the host rejects such ids; stay in bounds anyway
+    const T* src = table + (size_t)id * dim;
+    const T* pos = nullptr;
+    if (pos_table != nullptr) {
+        int p = positions[t];
+        (void)TL_CHECK(p >= 0 && p < n_positions, TL_DBG_POSITION);
+        p = p < 0 ? 0 : (p >= n_positions ? n_positions - 1 : p);
+        pos = pos_table + (size_t)p * dim;
+    }
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+        float v = to_float(src[d]) * scale;
+        if (pos != nullptr) v += to_float(pos[d]);
+        out[(size_t)t * dim + d] = v;
+        if (rows_out != nullptr) rows_out[(size_t)t * dim + d] = __float2bfloat16_rn(v);
+    }
+}
+
+__global__ void stream_rows_kernel(const float* __restrict__ h, __nv_bfloat16* __restrict__ out, long long n) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+        out[i] = __float2bfloat16_rn(h[i]);
+}
+
+// One CTA per row.  The summed delta is kept in shared memory between the two passes.
+template <typename TD>
+__global__ void norm_add_kernel(float* __restrict__ h, const TD* __restrict__ delta, int splits, long long plane,
+                                const float* __restrict__ weight, __nv_bfloat16* __restrict__ rows_out, int dim,
+                                float eps) {
+    extern __shared__ __align__(16) float row_buf[];
+    __shared__ float part[33];
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const size_t base = (size_t)blockIdx.x * dim;
+    float ssq = 0.f;
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+        float v = 0.f;
+        for (int s = 0; s < splits; ++s) v += to_float(delta[(size_t)s * plane + base + d]);
+        row_buf[d] = v;
+        ssq = fmaf(v, v, ssq);
+    }
+    const float total = block_sum(ssq, part);
+    const float r = rsqrtf(total / (float)dim + eps);
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+        const float v = h[base + d] + row_buf[d] * r * weight[d];
+        h[base + d] = v;
+        if (rows_out != nullptr) rows_out[base + d] = __float2bfloat16_rn(v);
+    }
+}
+
+template <typename TI, typename TO>
+__global__ void glu_clamped_kernel(const TI* __restrict__ in, int splits, long long plane, TO* __restrict__ out,
+                                   long long n_tokens, int hidden, float limit, float alpha, float up_offset) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const long long total = n_tokens * hidden;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long t = i / hidden;
+        const int f = (int)(i - t * hidden);
+        const size_t at = (size_t)t * 2 * hidden + f;
+        float g = 0.f, u = 0.f;
+        for (int s = 0; s < splits; ++s) {
+            g += to_float(in[(size_t)s * plane + at]);
+            u += to_float(in[(size_t)s * plane + at + hidden]);
+        }
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        out[i] = from_float<TO>(g / (1.f + expf(-alpha * g)) * (u + up_offset));
+    }
+}
+
+struct ProjectParams {
+    const void* proj;       // [splits][T][width]
+    int splits;
+    long long plane;
+    const float* bias;      // [width] or null
+    const float* q_norm;    // [n_q] or null
+    const float* k_norm;    // [n_k] or null
+    float eps;
+    int n_q, n_k, n_v, n_extra;
+    void* q_out;            // [T, n_q]
+    void* extra_out;        // [T, n_extra]
+    void* k_pages;          // [pages, kv_heads, page_size, k_dim] or null
+    void* v_pages;          // [pages, kv_heads, page_size, v_dim] or null
+    const int* slot_mapping;
+    int page_size, n_kv_heads, k_dim, v_dim;
+};
+
+// One CTA per token; the row in shared memory as float32.
+template <typename TI, typename TO>
+__global__ void project_store_kernel(const ProjectParams p) {
+    extern __shared__ __align__(16) float row[];
+    __shared__ float part[33];
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const int t = blockIdx.x;
+    const int width = p.n_q + p.n_k + p.n_v + p.n_extra;
+    const TI* in = reinterpret_cast<const TI*>(p.proj) + (size_t)t * width;
+    float ssq_q = 0.f, ssq_k = 0.f;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        float v = 0.f;
+        for (int s = 0; s < p.splits; ++s) v += to_float(in[(size_t)s * p.plane + c]);
+        if (p.bias != nullptr) v += p.bias[c];
+        row[c] = v;
+        if (c < p.n_q) ssq_q = fmaf(v, v, ssq_q);
+        else if (c < p.n_q + p.n_k) ssq_k = fmaf(v, v, ssq_k);
+    }
+    float rq = 1.f, rk = 1.f;
+    if (p.q_norm != nullptr) rq = rsqrtf(block_sum(ssq_q, part) / (float)p.n_q + p.eps);
+    if (p.k_norm != nullptr && p.n_k > 0) rk = rsqrtf(block_sum(ssq_k, part) / (float)p.n_k + p.eps);
+    __syncthreads();
+
+    TO* q_out = reinterpret_cast<TO*>(p.q_out) + (size_t)t * p.n_q;
+    for (int c = threadIdx.x; c < p.n_q; c += blockDim.x)
+        q_out[c] = from_float<TO>(p.q_norm != nullptr ? row[c] * rq * p.q_norm[c] : row[c]);
+
+    if (p.k_pages != nullptr && p.n_k > 0) {
+        const int slot = p.slot_mapping[t];
+        if (TL_CHECK(slot >= 0, TL_DBG_SLOT) && tl_check_page(slot / p.page_size)) {
+            const size_t page = slot / p.page_size, off = slot % p.page_size;
+            TO* kp = reinterpret_cast<TO*>(p.k_pages);
+            const float* k = row + p.n_q;
+            for (int c = threadIdx.x; c < p.n_k; c += blockDim.x) {
+                const int head = c / p.k_dim, d = c - head * p.k_dim;
+                const float v = p.k_norm != nullptr ? k[c] * rk * p.k_norm[c] : k[c];
+                kp[((page * p.n_kv_heads + head) * p.page_size + off) * p.k_dim + d] = from_float<TO>(v);
+            }
+            if (p.v_pages != nullptr && p.n_v > 0) {
+                TO* vp = reinterpret_cast<TO*>(p.v_pages);
+                const float* v = row + p.n_q + p.n_k;
+                for (int c = threadIdx.x; c < p.n_v; c += blockDim.x) {
+                    const int head = c / p.v_dim, d = c - head * p.v_dim;
+                    vp[((page * p.n_kv_heads + head) * p.page_size + off) * p.v_dim + d] = from_float<TO>(v[c]);
+                }
+            }
+        }
+    }
+    if (p.n_extra > 0) {
+        TO* e_out = reinterpret_cast<TO*>(p.extra_out) + (size_t)t * p.n_extra;
+        const float* e = row + p.n_q + p.n_k + p.n_v;
+        for (int c = threadIdx.x; c < p.n_extra; c += blockDim.x) e_out[c] = from_float<TO>(1.f / (1.f + expf(-e[c])));
+    }
+}
+
+inline int row_threads(int dim) { return dim >= 2048 ? 512 : (dim >= 512 ? 256 : 128); }
+
+}  // namespace
+
+// table and pos_table have one dtype; positions and pos_table may be null (no position table);
+// rows_out (bfloat16) may be null.
+extern "C" int tl_embed_positions(const int* ids, const int* positions, const void* table, const void* pos_table,
+                                  int table_dtype, float scale, float* out, void* rows_out, int n_tokens, int dim,
+                                  int vocab, int n_positions, void* stream) {
+    if (n_tokens <= 0) return TL_OK;
+    if (dim <= 0 || vocab <= 0 || (pos_table != nullptr && (positions == nullptr || n_positions <= 0))) return TL_BAD_SIZE;
+    cudaStream_t s = (cudaStream_t)stream;
+    cudaError_t e;
+    if (table_dtype == TL_F32)
+        e = tl_launch(embed_positions_kernel<float>, dim3(n_tokens), dim3(row_threads(dim)), 0, s, ids, positions,
+                      (const float*)table, (const float*)pos_table, scale, out, (__nv_bfloat16*)rows_out, dim, vocab,
+                      n_positions);
+    else if (table_dtype == TL_BF16)
+        e = tl_launch(embed_positions_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(row_threads(dim)), 0, s, ids, positions,
+                      (const __nv_bfloat16*)table, (const __nv_bfloat16*)pos_table, scale, out, (__nv_bfloat16*)rows_out,
+                      dim, vocab, n_positions);
+    else
+        return TL_BAD_DTYPE;
+    return (int)e;
+}
+
+extern "C" int tl_stream_rows(const float* h, void* out, long long n, void* stream) {
+    if (n <= 0) return TL_OK;
+    long long blocks = (n + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    return (int)tl_launch(stream_rows_kernel, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, h,
+                          (__nv_bfloat16*)out, n);
+}
+
+// delta: [splits][n_rows][dim] in delta_dtype, planes `plane` elements apart; rows_out (bfloat16) may be null.
+extern "C" int tl_norm_add(float* h, const void* delta, int delta_dtype, int splits, long long plane,
+                           const float* weight, void* rows_out, int n_rows, int dim, float eps, void* stream) {
+    if (n_rows <= 0) return TL_OK;
+    if (dim <= 0 || splits < 1) return TL_BAD_SIZE;
+    const size_t smem = (size_t)dim * sizeof(float);
+    if (smem > 200 * 1024) return TL_TOO_LARGE;
+    cudaStream_t s = (cudaStream_t)stream;
+    cudaError_t e;
+    if (delta_dtype == TL_F32) {
+        static int raised = 0;
+        if (smem > 48 * 1024 && (int)smem > raised) {
+            e = cudaFuncSetAttribute(norm_add_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return (int)e;
+            raised = (int)smem;
+        }
+        e = tl_launch(norm_add_kernel<float>, dim3(n_rows), dim3(row_threads(dim)), smem, s, h, (const float*)delta, splits,
+                      plane, weight, (__nv_bfloat16*)rows_out, dim, eps);
+    } else if (delta_dtype == TL_BF16) {
+        static int raised = 0;
+        if (smem > 48 * 1024 && (int)smem > raised) {
+            e = cudaFuncSetAttribute(norm_add_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return (int)e;
+            raised = (int)smem;
+        }
+        e = tl_launch(norm_add_kernel<__nv_bfloat16>, dim3(n_rows), dim3(row_threads(dim)), smem, s, h,
+                      (const __nv_bfloat16*)delta, splits, plane, weight, (__nv_bfloat16*)rows_out, dim, eps);
+    } else {
+        return TL_BAD_DTYPE;
+    }
+    return (int)e;
+}
+
+// in: [splits][n_tokens][2 * hidden] (gate columns first); out: [n_tokens][hidden].
+extern "C" int tl_glu_clamped(const void* in, int in_dtype, int splits, long long plane, void* out, int out_dtype,
+                              int n_tokens, int hidden, float limit, float alpha, float up_offset, void* stream) {
+    if ((long long)n_tokens * hidden <= 0) return TL_OK;
+    if (splits < 1) return TL_BAD_SIZE;
+    cudaStream_t s = (cudaStream_t)stream;
+    long long blocks = ((long long)n_tokens * hidden + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    const dim3 grid((unsigned)blocks), block(256);
+    cudaError_t e;
+    if (in_dtype == TL_F32 && out_dtype == TL_F32)
+        e = tl_launch(glu_clamped_kernel<float, float>, grid, block, 0, s, (const float*)in, splits, plane, (float*)out,
+                      (long long)n_tokens, hidden, limit, alpha, up_offset);
+    else if (in_dtype == TL_F32 && out_dtype == TL_BF16)
+        e = tl_launch(glu_clamped_kernel<float, __nv_bfloat16>, grid, block, 0, s, (const float*)in, splits, plane,
+                      (__nv_bfloat16*)out, (long long)n_tokens, hidden, limit, alpha, up_offset);
+    else if (in_dtype == TL_BF16 && out_dtype == TL_BF16)
+        e = tl_launch(glu_clamped_kernel<__nv_bfloat16, __nv_bfloat16>, grid, block, 0, s, (const __nv_bfloat16*)in, splits,
+                      plane, (__nv_bfloat16*)out, (long long)n_tokens, hidden, limit, alpha, up_offset);
+    else
+        return TL_BAD_DTYPE;
+    return (int)e;
+}
+
+extern "C" int tl_project_store(const void* proj, int in_dtype, int splits, long long plane, const float* bias,
+                                const float* q_norm, const float* k_norm, float eps, int n_q, int n_k, int n_v,
+                                int n_extra, void* q_out, void* extra_out, int out_dtype, void* k_pages, void* v_pages,
+                                const int* slot_mapping, int page_size, int n_kv_heads, int k_dim, int v_dim,
+                                int n_tokens, void* stream) {
+    if (n_tokens <= 0) return TL_OK;
+    if (n_q < 0 || n_k < 0 || n_v < 0 || n_extra < 0 || splits < 1) return TL_BAD_SIZE;
+    const int width = n_q + n_k + n_v + n_extra;
+    if (width <= 0) return TL_BAD_SIZE;
+    if (k_pages != nullptr && n_k > 0 &&
+        (slot_mapping == nullptr || page_size <= 0 || n_kv_heads <= 0 || k_dim <= 0 || n_k != n_kv_heads * k_dim))
+        return TL_BAD_SIZE;
+    if (k_pages != nullptr && v_pages != nullptr && n_v > 0 && (v_dim <= 0 || n_v != n_kv_heads * v_dim)) return TL_BAD_SIZE;
+    const size_t smem = (size_t)width * sizeof(float);
+    if (smem > 200 * 1024) return TL_TOO_LARGE;
+    ProjectParams p;
+    p.proj = proj; p.splits = splits; p.plane = plane; p.bias = bias; p.q_norm = q_norm; p.k_norm = k_norm; p.eps = eps;
+    p.n_q = n_q; p.n_k = n_k; p.n_v = n_v; p.n_extra = n_extra; p.q_out = q_out; p.extra_out = extra_out;
+    p.k_pages = k_pages; p.v_pages = v_pages; p.slot_mapping = slot_mapping; p.page_size = page_size;
+    p.n_kv_heads = n_kv_heads; p.k_dim = k_dim; p.v_dim = v_dim;
+    cudaStream_t s = (cudaStream_t)stream;
+    cudaError_t e;
+#define TL_PROJECT_LAUNCH(TI, TO)                                                                                      \
+    do {                                                                                                               \
+        static int raised = 0;                                                                                         \
+        if (smem > 48 * 1024 && (int)smem > raised) {                                                                  \
+            e = cudaFuncSetAttribute(project_store_kernel<TI, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            if (e != cudaSuccess) return (int)e;                                                                       \
+            raised = (int)smem;                                                                                        \
+        }                                                                                                              \
+        e = tl_launch(project_store_kernel<TI, TO>, dim3(n_tokens), dim3(row_threads(width)), smem, s, p);             \
+    } while (0)
+    if (in_dtype == TL_F32 && out_dtype == TL_F32) TL_PROJECT_LAUNCH(float, float);
+    else if (in_dtype == TL_F32 && out_dtype == TL_BF16) TL_PROJECT_LAUNCH(float, __nv_bfloat16);
+    else if (in_dtype == TL_BF16 && out_dtype == TL_BF16) TL_PROJECT_LAUNCH(__nv_bfloat16, __nv_bfloat16);
+    else return TL_BAD_DTYPE;
+#undef TL_PROJECT_LAUNCH
+    return (int)e;
+}

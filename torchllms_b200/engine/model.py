@@ -14,7 +14,7 @@ from typing import Dict, List, Mapping, Optional, Sequence, Tuple
 
 import torch
 
-from ..parts import attention, block, ffn, norm, rope  # noqa: F401  (register the built-in parts)
+from ..parts import attention, block, ffn, latent_attention, norm, rope  # noqa: F401  (register the built-in parts)
 from ..parts.base import BLOCKS, NORMS, BuildEnv, CacheNeed, Residual, StateNeed, as_compute
 from ..parts.spec import ModelSpec
 from ..weights.loader import ExpectedTensor
@@ -29,18 +29,24 @@ class Model:
         self.device = torch.device(device)
         self.ops = ops
         self.max_positions = int(max_positions or spec.max_positions)
+        if spec.position_tensor is not None:
+            # a learned position table ends where it ends: no request can grow past its last row
+            self.max_positions = min(self.max_positions, spec.max_positions)
         self.env = BuildEnv(dim=spec.dim, dtype=dtype, device=self.device,
                             max_positions=self.max_positions, ops=ops)
         self.blocks = [BLOCKS.build(layer.block, self.env) for layer in spec.layers]
         self.final_norm = NORMS.build(spec.final_norm, self.env)
         self.graph_safe = self.final_norm.graph_safe and all(b.graph_safe for b in self.blocks)
         self.embedding: Optional[torch.Tensor] = None
+        self.position_table: Optional[torch.Tensor] = None
         self.head: Optional[torch.Tensor] = None
 
     # ----------------------------------------------------------------- weights
     def expected_tensors(self) -> Dict[str, ExpectedTensor]:
         spec = self.spec
         out: Dict[str, ExpectedTensor] = {spec.embedding_tensor: ExpectedTensor((spec.vocab_size, spec.dim))}
+        if spec.position_tensor is not None:
+            out[spec.position_tensor] = ExpectedTensor((spec.max_positions, spec.dim))
         for layer, blk in zip(spec.layers, self.blocks):
             for name, e in blk.expected_tensors().items():
                 out[f"{layer.name}.{name}"] = e
@@ -54,6 +60,8 @@ class Model:
         """``tensors`` holds exactly :meth:`expected_tensors` (checked by the caller)."""
         spec = self.spec
         self.embedding = as_compute(tensors[spec.embedding_tensor], self.env)
+        if spec.position_tensor is not None:
+            self.position_table = as_compute(tensors[spec.position_tensor], self.env)
         for layer, blk in zip(spec.layers, self.blocks):
             blk.load({name: tensors[f"{layer.name}.{name}"] for name in blk.expected_tensors()})
         self.final_norm.load({name: tensors[f"{spec.final_norm_prefix}.{name}"]
@@ -75,7 +83,11 @@ class Model:
     # ----------------------------------------------------------------- forward
     def forward(self, ctx, views: Sequence) -> Optional[torch.Tensor]:
         """Run the step's tokens; returns float32 logits ``[n_wanted, vocab]`` or ``None``."""
-        h = self.ops.embed(ctx.token_ids, self.embedding)
+        if self.position_table is None and self.spec.embedding_scale == 1.0:
+            h = self.ops.embed(ctx.token_ids, self.embedding)
+        else:
+            h = self.ops.embed(ctx.token_ids, self.embedding, scale=self.spec.embedding_scale,
+                               positions=ctx.positions, position_table=self.position_table)
         residual = Residual(h)
         for i, run in enumerate(self.spec.run_order):
             self.blocks[run.layer].forward(residual, ctx, views[i])

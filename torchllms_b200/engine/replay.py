@@ -47,8 +47,9 @@ class Replayer:
         max_positions = max(int(config.max_seq_len), round_up(max_tokens, page_size))
         _, self.config, model = load_model(model_dir, dtype=dtype, device=device, ops=ops,
                                            max_positions=max_positions)
+        # (a model with a learned position table ends where its table ends, whatever was asked for)
         self.engine = Engine(model, page_size=page_size, pool_tokens=round_up(max_tokens, page_size),
-                             max_num_seqs=max_num_seqs, max_len=max_positions,
+                             max_num_seqs=max_num_seqs, max_len=model.max_positions,
                              max_step_tokens=max(round_up(max_tokens, page_size), 64))
         self.handles: Dict[str, int] = {}
 
@@ -84,10 +85,11 @@ def main(argv=None) -> int:
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens live requests hold at any time (each rounded up to 64)")
     ap.add_argument("--page-size", type=int, default=16)
+    ap.add_argument("--max-requests", type=int, default=4, help="how many requests may be live at a time (state slots)")
     args = ap.parse_args(argv)
     out = Path(args.out)
     out.mkdir(parents=True, exist_ok=True)
-    replayer = Replayer(args.model, args.dtype, args.max_tokens, page_size=args.page_size)
+    replayer = Replayer(args.model, args.dtype, args.max_tokens, page_size=args.page_size, max_num_seqs=args.max_requests)
     for line in sys.stdin:
         line = line.strip()
         if not line:

@@ -91,12 +91,13 @@ class LLM:
                 config, random_seed or 0, dtype=self.dtype, device=device, max_positions=max_len, ops=ops)
         else:
             raise ValueError("give ckpt_paths (a model folder) or config and random_seed")
-        self.max_len = int(max_len)
+        self.max_len = min(int(max_len), self.model.max_positions)     # (a learned position table ends where it ends)
         self.max_bsz = int(max_bsz)
         self.device = device
         self.seed = int(seed)
         self.batched = batched
-        bytes_per_token = sum(g_need.n_kv_heads * g_need.head_dim * 2 * n_runs for g_need, n_runs in self._kv_layout())
+        bytes_per_token = sum(g_need.n_kv_heads * (g_need.head_dim + g_need.value_dim) * n_runs
+                              for g_need, n_runs in self._kv_layout())
         bytes_per_token *= torch.empty((), dtype=self.dtype).element_size()
         if kv_memory_gb is not None and kv_memory_fraction is not None:
             raise ValueError("give kv_memory_gb or kv_memory_fraction, not both")

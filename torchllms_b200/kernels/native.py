@@ -148,7 +148,7 @@ class NativeOps:
     # ------------------------------------------------------------ libraries
     def prepare(self, dtype: torch.dtype, sampling: bool = True) -> None:
         """Compile, side by side, what a model of this dtype will call."""
-        names = ["elementwise", "rope", "attention", "gemm_simt"]
+        names = ["elementwise", "sublayer", "rope", "attention", "gemm_simt"]
         if dtype == torch.bfloat16:
             names += ["attention_mma", "attention_decode", "gemm_tcgen05"]
         if sampling:
@@ -178,21 +178,40 @@ class NativeOps:
                 inner[depth] = inner.get(depth, 0.0) + ms
 
     # ------------------------------------------------------------- checks
-    def check_attention_sizes(self, n_heads: int, n_kv_heads: int, head_dim: int, dtype: torch.dtype) -> None:
+    def check_attention_sizes(self, n_heads: int, n_kv_heads: int, head_dim: int, dtype: torch.dtype,
+                              v_head_dim: Optional[int] = None) -> None:
+        """The general kernel takes any head size up to 256 (keys and values separately); the
+        tensor-core kernels take their own few sizes and are chosen only where they apply."""
         _need(dtype in _DT, f"attention supports float32 and bfloat16, not {dtype}")
         _need(n_heads > 0 and n_kv_heads > 0 and n_heads % n_kv_heads == 0,
               f"n_heads ({n_heads}) must be a positive multiple of n_kv_heads ({n_kv_heads})")
-        _need(head_dim % 16 == 0 and 16 <= head_dim <= 256,
-              f"head_dim must be a multiple of 16 between 16 and 256, got {head_dim}")
+        _need(1 <= head_dim <= 256, f"head_dim must lie between 1 and 256, got {head_dim}")
+        _need(v_head_dim is None or 1 <= v_head_dim <= 256, f"v_head_dim must lie between 1 and 256, got {v_head_dim}")
 
     # ------------------------------------------------------------ elementwise
     @_timed
-    def embed(self, token_ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
+    def embed(self, token_ids: torch.Tensor, table: torch.Tensor, scale: float = 1.0,
+              positions: Optional[torch.Tensor] = None, position_table: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``table[ids]`` as the float32 stream; with ``scale`` and a learned ``position_table``:
+        ``table[ids] * scale + position_table[positions]``."""
         _cuda_contig(token_ids, "token_ids", torch.int32)
         _cuda_contig(table, "embedding table")
         _need(table.dtype in _DT and table.dim() == 2, "embedding table must be a float32/bfloat16 matrix")
         n, (vocab, dim) = token_ids.numel(), table.shape
         out = torch.empty((n, dim), dtype=torch.float32, device=table.device)
+        if position_table is not None or scale != 1.0:
+            if position_table is not None:
+                _cuda_contig(position_table, "position table", table.dtype)
+                _cuda_contig(positions, "positions", torch.int32)
+                _need(position_table.dim() == 2 and position_table.shape[1] == dim and positions.numel() == n,
+                      "position table must be [positions, width], with one position per token")
+            rc = self._lib("sublayer").tl_embed_positions(
+                _ptr(token_ids), _ptr(positions if position_table is not None else None), _ptr(table), _ptr(position_table),
+                _DT[table.dtype], ctypes.c_float(scale), _ptr(out), _ptr(None), n, dim, vocab,
+                0 if position_table is None else position_table.shape[0], _stream())
+            _check(rc, "embed_positions")
+            self.launches += 1
+            return out
         rc = self._lib("elementwise").tl_embed(_ptr(token_ids), _ptr(table), _DT[table.dtype], _ptr(out),
                                               n, dim, vocab, _stream())
         _check(rc, "embed")
@@ -238,6 +257,136 @@ class NativeOps:
         _check(rc, "rmsnorm")
         self.launches += 1
         return RowScaled(out, ssq, dim, float(eps)) if deferred else out
+
+    @_timed
+    def stream_rows(self, h: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+        """The float32 stream as a sublayer's input: itself in 32-bit mode, rounded once otherwise."""
+        _cuda_contig(h, "residual stream", torch.float32)
+        if dtype == torch.float32:
+            return h
+        _need(dtype == torch.bfloat16, f"stream_rows: dtype {dtype} unsupported")
+        out = torch.empty(h.shape, dtype=dtype, device=h.device)
+        _check(self._lib("sublayer").tl_stream_rows(_ptr(h), _ptr(out), ctypes.c_longlong(h.numel()), _stream()), "stream_rows")
+        self.launches += 1
+        return out
+
+    @_timed
+    def norm_add(self, h: torch.Tensor, delta, weight: torch.Tensor, eps: float, out_dtype: torch.dtype) -> torch.Tensor:
+        """``h += delta / sqrt(mean(delta^2) + eps) * weight`` in place (float32): the norm of a
+        sublayer's output and the residual sum in one kernel.  ``delta`` is a tensor, float32
+        partial sums ``[splits, T, dim]`` or a :class:`PendingProduct`.  Returns the new stream in
+        ``out_dtype`` (``h`` itself for float32)."""
+        if isinstance(delta, PendingProduct):
+            delta = delta.take(self)
+        _cuda_contig(h, "residual stream", torch.float32)
+        _cuda_contig(weight, "norm weight", torch.float32)
+        _cuda_contig(delta, "delta")
+        _need(h.dim() == 2 and weight.numel() == h.shape[1], "norm weight must match the stream's width")
+        _need(delta.dtype in _DT and out_dtype in _DT, "norm_add: float32 or bfloat16")
+        T, dim = h.shape
+        _need(dim * 4 <= 200 * 1024, f"norm_add keeps a row in shared memory: width {dim} exceeds 51200")
+        splits, plane = 1, 0
+        if delta.dim() == 3:
+            _need(delta.shape[1:] == h.shape and delta.dtype == torch.float32, "partial sums must be float32 [splits, tokens, width]")
+            splits, plane = delta.shape[0], delta.stride(0)
+        else:
+            _need(delta.shape == h.shape, "delta must have the stream's shape")
+        rows = None if out_dtype == torch.float32 else torch.empty((T, dim), dtype=out_dtype, device=h.device)
+        rc = self._lib("sublayer").tl_norm_add(_ptr(h), _ptr(delta), _DT[delta.dtype], splits, ctypes.c_longlong(plane),
+                                              _ptr(weight), _ptr(rows), T, dim, ctypes.c_float(eps), _stream())
+        _check(rc, "norm_add")
+        self.launches += 1
+        return h if rows is None else rows
+
+    @_timed
+    def glu(self, gate_up: torch.Tensor, out_dtype: Optional[torch.dtype] = None, *, limit: float, alpha: float,
+            up_offset: float) -> torch.Tensor:
+        """``g * sigmoid(alpha g) * (u + up_offset)`` with ``g = min(gate, limit)``, ``u = clamp(up, +-limit)``;
+        ``gate_up`` is ``[tokens, 2 * hidden]`` or float32 partial sums of it."""
+        _cuda_contig(gate_up, "gate_up")
+        _need(gate_up.dim() in (2, 3) and gate_up.shape[-1] % 2 == 0 and gate_up.dtype in _DT,
+              "glu input must be [tokens, 2 * hidden] in float32/bfloat16")
+        splits = gate_up.shape[0] if gate_up.dim() == 3 else 1
+        _need(splits == 1 or gate_up.dtype == torch.float32, "partial sums must be float32")
+        out_dtype = out_dtype or gate_up.dtype
+        _need(out_dtype in _DT and (out_dtype == gate_up.dtype or gate_up.dtype == torch.float32), "glu cannot widen bfloat16 input")
+        n, hidden = gate_up.shape[-2], gate_up.shape[-1] // 2
+        out = torch.empty((n, hidden), dtype=out_dtype, device=gate_up.device)
+        rc = self._lib("sublayer").tl_glu_clamped(
+            _ptr(gate_up), _DT[gate_up.dtype], splits, ctypes.c_longlong(gate_up.stride(0) if splits > 1 else 0), _ptr(out),
+            _DT[out_dtype], n, hidden, ctypes.c_float(limit), ctypes.c_float(alpha), ctypes.c_float(up_offset), _stream())
+        _check(rc, "glu_clamped")
+        self.launches += 1
+        return out
+
+    def linear_glu(self, x: torch.Tensor, w_gate_up: torch.Tensor, *, limit: float, alpha: float, up_offset: float) -> torch.Tensor:
+        """The gate/up product over the stacked weight ``[2 H, K]`` and the clamped gate, in ``x``'s dtype."""
+        return self.glu(self.linear(x, w_gate_up, partials_ok=True), out_dtype=x.dtype, limit=limit, alpha=alpha,
+                        up_offset=up_offset)
+
+    @_timed
+    def project_and_store(self, proj: torch.Tensor, *, n_q: int, n_k: int, n_v: int, n_extra: int,
+                          bias: Optional[torch.Tensor], q_norm: Optional[torch.Tensor], k_norm: Optional[torch.Tensor],
+                          eps: float, k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor],
+                          slot_mapping: Optional[torch.Tensor], page_size: int, out_dtype: torch.dtype):
+        """What follows a mixer's stacked input projection, whose rows are ``[q | k | v | extra]``
+        (``proj`` is ``[T, width]`` or float32 partial sums ``[splits, T, width]``): the bias is
+        added, q and k are each RMS-normed over their whole width where a weight is given, k and v
+        go into their pages at ``slot_mapping`` (``k_pages`` ``[pages, kv_heads, page_size, k_dim]``,
+        ``v_pages`` likewise or ``None``), and ``q`` and ``sigmoid(extra)`` come back in ``out_dtype``."""
+        _cuda_contig(proj, "projection")
+        width = n_q + n_k + n_v + n_extra
+        _need(proj.dim() in (2, 3) and proj.shape[-1] == width and proj.dtype in _DT, "projection rows must be [q | k | v | extra]")
+        splits = proj.shape[0] if proj.dim() == 3 else 1
+        _need(splits == 1 or proj.dtype == torch.float32, "partial sums must be float32")
+        _need(out_dtype in _DT and (out_dtype == proj.dtype or proj.dtype == torch.float32), "project_and_store cannot widen bfloat16 input")
+        _need(width * 4 <= 200 * 1024, f"project_and_store keeps a row in shared memory: {width} columns exceed 51200")
+        T = proj.shape[-2]
+        for t, n, name in ((bias, width, "bias"), (q_norm, n_q, "q_norm"), (k_norm, n_k, "k_norm")):
+            if t is not None:
+                _cuda_contig(t, name, torch.float32)
+                _need(t.numel() == n, f"{name} must have {n} elements")
+        kvh = kd = vd = 0
+        if k_pages is not None and n_k:
+            _cuda_contig(k_pages, "k_pages", out_dtype)
+            _cuda_contig(slot_mapping, "slot_mapping", torch.int32)
+            _need(k_pages.dim() == 4 and k_pages.shape[2] == page_size and k_pages.shape[1] * k_pages.shape[3] == n_k,
+                  "k_pages must be [pages, kv_heads, page_size, k_dim] with kv_heads * k_dim key columns")
+            _need(slot_mapping.numel() == T, "one cache slot per token")
+            kvh, kd = k_pages.shape[1], k_pages.shape[3]
+            if v_pages is not None and n_v:
+                _cuda_contig(v_pages, "v_pages", out_dtype)
+                _need(v_pages.dim() == 4 and v_pages.shape[:3] == k_pages.shape[:3] and kvh * v_pages.shape[3] == n_v,
+                      "v_pages must be [pages, kv_heads, page_size, v_dim] with kv_heads * v_dim value columns")
+                vd = v_pages.shape[3]
+            self._debug_limit("sublayer", 0, k_pages.shape[0])
+        else:
+            k_pages = v_pages = None
+        q = torch.empty((T, n_q), dtype=out_dtype, device=proj.device)
+        extra = torch.empty((T, n_extra), dtype=out_dtype, device=proj.device) if n_extra else None
+        rc = self._lib("sublayer").tl_project_store(
+            _ptr(proj), _DT[proj.dtype], splits, ctypes.c_longlong(proj.stride(0) if splits > 1 else 0), _ptr(bias),
+            _ptr(q_norm), _ptr(k_norm), ctypes.c_float(eps), n_q, n_k, n_v, n_extra, _ptr(q), _ptr(extra), _DT[out_dtype],
+            _ptr(k_pages), _ptr(v_pages), _ptr(slot_mapping if k_pages is not None else None), page_size, kvh, kd, vd, T,
+            _stream())
+        _check(rc, "project_store")
+        self.launches += 1
+        return q, extra
+
+    @_timed
+    def head_linear(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+        """One small product per head: ``x [T, H, K]`` against ``w [H, N, K]`` gives ``[T, H, N]``,
+        ``out[t, h] = w[h] @ x[t, h]`` (float32 multiply-adds on the CUDA cores in both dtypes)."""
+        _cuda_contig(x, "head_linear input")
+        _cuda_contig(w, "head_linear weight", x.dtype)
+        _need(x.dim() == 3 and w.dim() == 3 and x.shape[1] == w.shape[0] and x.shape[2] == w.shape[2] and x.dtype in _DT,
+              "head_linear: x [T, H, K] against w [H, N, K]")
+        T, H, K = x.shape
+        N = w.shape[1]
+        out = torch.empty((T, H, N), dtype=x.dtype, device=x.device)
+        _check(self._lib("gemm_simt").tl_head_linear(_ptr(x), _ptr(w), _ptr(out), _DT[x.dtype], T, H, N, K, _stream()), "head_linear")
+        self.launches += 1
+        return out
 
     def can_fuse_residual(self, pending, h: torch.Tensor) -> bool:
         """Whether :meth:`linear_residual_norm` takes this pending product for this stream."""
@@ -508,7 +657,9 @@ class NativeOps:
                         n_seqs: int, max_q_len: int, max_kv_len: int, scale: float,
                         window: Optional[int], page_size: int, allow_split: bool = True,
                         impl: str = "auto", n_tokens: Optional[int] = None,
-                        out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                        out: Optional[torch.Tensor] = None, keep_first: int = 0,
+                        distance_bias: Optional[torch.Tensor] = None, distance_buckets: Optional[torch.Tensor] = None,
+                        gate: Optional[torch.Tensor] = None) -> torch.Tensor:
         """``impl``: ``"general"`` (CUDA cores, any supported size, both dtypes), ``"mma"`` (tensor
         cores, bfloat16, head_dim 16/32/64/128), ``"decode"`` (tensor cores fed by TMA, bfloat16,
         head_dim 64/128, steps whose requests bring one token or very few), ``"prefill"``
@@ -520,7 +671,20 @@ class NativeOps:
         the step (``q_start`` keeps counting tokens from the start of ``q``); ``n_tokens`` then
         bounds the rows those requests own (default: all of ``q``), and ``out`` lets several such
         calls fill one tensor.  ``allow_split``: False keeps every request's keys in one CTA, True lets
-        the kernel split them as it sees fit; the decode kernel also takes a number of splits (above 1)."""
+        the kernel split them as it sees fit; the decode kernel also takes a number of splits (above 1).
+
+        The general kernel alone also takes: values of another size than keys (``v_pages``
+        ``[pages, kv_heads, page_size, v_dim]``, possibly the very tensor ``k_pages``; the result is
+        ``[T, H, v_dim]``), ``keep_first`` (with a window: the first so many keys of a request stay
+        visible), ``distance_bias`` ``[rows, H]`` float32 with ``distance_buckets`` (int32: the
+        table's row for every distance), added to the scaled score, and ``gate`` (``[T, H]`` or
+        ``[T, H * v_dim]``, in q's dtype), by which the result is multiplied."""
+        if keep_first or distance_bias is not None or gate is not None or v_pages.shape[-1] != q.shape[-1] \
+                or q.shape[-1] % 16 != 0:
+            _need(impl in ("auto", "general"), "only the general attention kernel takes these options")
+            return self._paged_attention_general(q, k_pages, v_pages, block_table, q_start, kv_len, n_seqs, max_q_len,
+                                                 max_kv_len, scale, window, page_size, allow_split, n_tokens, out,
+                                                 keep_first, distance_bias, distance_buckets, gate)
         _cuda_contig(q, "q")
         _cuda_contig(k_pages, "k_pages", q.dtype)
         _cuda_contig(v_pages, "v_pages", q.dtype)
@@ -602,18 +766,71 @@ class NativeOps:
                 1 if allow_split else 0, _stream())
             _check(rc, "paged_attention_mma")
         else:
-            lib = self._lib("attention")
-            rc = lib.tl_attention_plan(T, n_seqs, n_heads, n_kv_heads, head_dim, max_q_len, max_kv_len,
-                                       1 if allow_split else 0, ctypes.byref(n_splits), ctypes.byref(floats))
-            _check(rc, "attention_plan")
-            ws = self._scratch(q.device, floats.value)
-            self._debug_limit("attention", 0, k_pages.shape[0])
-            rc = lib.tl_paged_attention(
-                _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(block_table), block_table.stride(0),
-                _ptr(q_start), _ptr(kv_len), _ptr(ws), _DT[q.dtype], T, n_seqs, n_heads, n_kv_heads, head_dim,
-                page_size, max_q_len, max_kv_len, int(window or 0), ctypes.c_float(scale),
-                1 if allow_split else 0, _stream())
-            _check(rc, "paged_attention")
+            return self._paged_attention_general(q, k_pages, v_pages, block_table, q_start, kv_len, n_seqs, max_q_len,
+                                                 max_kv_len, scale, window, page_size, allow_split, n_tokens, out,
+                                                 0, None, None, None)
+        self.launches += 2 if n_splits.value > 1 else 1
+        return out
+
+    class _AttentionOptions(ctypes.Structure):
+        _fields_ = [("v_head_dim", ctypes.c_int), ("keep_first", ctypes.c_int), ("rel", ctypes.c_void_p),
+                    ("bucket", ctypes.c_void_p), ("n_bucket", ctypes.c_int), ("gate", ctypes.c_void_p),
+                    ("gate_mode", ctypes.c_int)]
+
+    def _paged_attention_general(self, q, k_pages, v_pages, block_table, q_start, kv_len, n_seqs, max_q_len, max_kv_len,
+                                 scale, window, page_size, allow_split, n_tokens, out, keep_first, distance_bias,
+                                 distance_buckets, gate) -> torch.Tensor:
+        """The CUDA-core kernel with everything it can do (see :meth:`paged_attention`)."""
+        _cuda_contig(q, "q")
+        _cuda_contig(k_pages, "k_pages", q.dtype)
+        _cuda_contig(v_pages, "v_pages", q.dtype)
+        _cuda_contig(q_start, "q_start", torch.int32)
+        _cuda_contig(kv_len, "kv_len", torch.int32)
+        _need(block_table.is_cuda and block_table.dtype == torch.int32 and block_table.dim() == 2
+              and block_table.stride(1) == 1, "block_table must be an int32 matrix with unit column stride")
+        T_all, n_heads, head_dim = q.shape
+        T = T_all if n_tokens is None else int(n_tokens)
+        _need(0 < T <= T_all, "n_tokens must lie within q")
+        n_kv_heads, v_dim = k_pages.shape[1], v_pages.shape[3]
+        self.check_attention_sizes(n_heads, n_kv_heads, head_dim, q.dtype, v_dim)
+        _need(k_pages.shape[2] == page_size and k_pages.shape[3] == head_dim and v_pages.shape[:3] == k_pages.shape[:3],
+              "pages must be [pages, n_kv_heads, page_size, head_dim] (values: their own last size)")
+        _need(block_table.shape[0] >= n_seqs and q_start.numel() >= n_seqs + 1 and kv_len.numel() >= n_seqs,
+              "block_table, q_start and kv_len must cover every request of the step")
+        _need(block_table.shape[1] * page_size >= max_kv_len, "block_table is too narrow for max_kv_len")
+        _need(keep_first >= 0 and (not keep_first or window), "keep_first goes with a window")
+        if out is None:
+            out = torch.empty((T_all, n_heads, v_dim), dtype=q.dtype, device=q.device)
+        else:
+            _cuda_contig(out, "out", q.dtype)
+            _need(out.shape == (T_all, n_heads, v_dim), "out must be [tokens, heads, v_dim]")
+        opt = self._AttentionOptions(v_dim, int(keep_first), None, None, 0, None, 0)
+        if distance_bias is not None:
+            _cuda_contig(distance_bias, "distance_bias", torch.float32)
+            _cuda_contig(distance_buckets, "distance_buckets", torch.int32)
+            _need(distance_bias.dim() == 2 and distance_bias.shape[1] == n_heads, "distance_bias must be [rows, n_heads]")
+            _need(distance_buckets.numel() >= min(max_kv_len, block_table.shape[1] * page_size),
+                  "distance_buckets must reach as far as the longest context")
+            opt.rel, opt.bucket, opt.n_bucket = distance_bias.data_ptr(), distance_buckets.data_ptr(), distance_buckets.numel()
+        if gate is not None:
+            _cuda_contig(gate, "gate", q.dtype)
+            _need(gate.dim() == 2 and gate.shape[0] == T_all and gate.shape[1] in (n_heads, n_heads * v_dim),
+                  "gate must be [tokens, heads] or [tokens, heads * v_dim]")
+            opt.gate, opt.gate_mode = gate.data_ptr(), (1 if gate.shape[1] == n_heads and v_dim != 1 else 2)
+        n_splits, floats = ctypes.c_int(0), ctypes.c_longlong(0)
+        lib = self._lib("attention")
+        rc = lib.tl_attention_plan_ex(T, n_seqs, n_heads, n_kv_heads, head_dim, v_dim, max_q_len, max_kv_len,
+                                      int(window or 0), int(keep_first), 1 if allow_split else 0,
+                                      ctypes.byref(n_splits), ctypes.byref(floats))
+        _check(rc, "attention_plan")
+        ws = self._scratch(q.device, floats.value)
+        self._debug_limit("attention", 0, k_pages.shape[0])
+        rc = lib.tl_paged_attention_ex(
+            _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(block_table), block_table.stride(0),
+            _ptr(q_start), _ptr(kv_len), _ptr(ws), _DT[q.dtype], T, n_seqs, n_heads, n_kv_heads, head_dim,
+            page_size, max_q_len, max_kv_len, int(window or 0), ctypes.c_float(scale),
+            1 if allow_split else 0, ctypes.byref(opt), _stream())
+        _check(rc, "paged_attention")
         self.launches += 2 if n_splits.value > 1 else 1
         return out
 

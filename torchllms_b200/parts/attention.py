@@ -12,6 +12,7 @@ treats prompt portions and single decoded tokens alike.
 
 from __future__ import annotations
 
+import math
 from typing import Dict, Mapping, Optional
 
 import torch
@@ -88,3 +89,132 @@ class PagedAttention(Mixer):
         # the output projection is left to the norm that follows: it may add the product to the
         # residual stream in the product's own kernel, or take it and add up its partial sums
         return PendingProduct(o.view(o.shape[0], self.n_heads * self.head_dim), self.wo)
+
+
+def distance_buckets(n_rows: int, far: float, n_positions: int) -> torch.Tensor:
+    """``[n_positions]`` int32: the row of a distance-bias table for a key ``n`` places back.
+    Distances below half the rows have a row each; from there the rows are spread evenly over
+    ``ln(n)`` up to the distance ``far``; everything beyond falls into the last row:
+
+        ``row(n) = n``                                                              for ``n < n_rows // 2``
+        ``row(n) = min(n_rows - 1, half + floor(ln(n / half) / ln(far / half) * (n_rows - half)))``   otherwise
+
+    Tabulated once on the host (64-bit logarithms); the attention kernels look a distance up."""
+    half = n_rows // 2
+    if half < 1 or not far > half:
+        raise ValueError(f"a distance-bias table needs at least two rows and a far distance above {half}, got {n_rows} and {far}")
+    out = []
+    for n in range(n_positions):
+        if n < half:
+            out.append(n)
+        else:
+            out.append(min(n_rows - 1, half + int(math.floor(math.log(n / half) / math.log(far / half) * (n_rows - half)))))
+    return torch.tensor(out, dtype=torch.int32)
+
+
+@register_mixer("gated_attention")
+class GatedBiasedAttention(Mixer):
+    """Grouped-query attention without rotation, for designs that put positions elsewhere:
+
+    * projections ``wq, wk, wv`` with optional biases (``qkv_bias``), keys and values of different
+      sizes (``head_dim``, ``v_head_dim``);
+    * optionally an RMS norm over the *whole* projected row of q and of k (``qk_norm``: before the
+      row is cut into heads; plain weights ``q_norm.weight``, ``k_norm.weight``);
+    * score ``= q . k * scale`` plus, with ``distance_bias``, a learned bias by distance and head
+      (tensor ``distance_bias`` ``[rows, n_heads]``, row chosen by :func:`distance_buckets`; the scale
+      does not touch it; ``bias_rows=None`` takes the number of rows from the stored table);
+    * a sliding window that may keep a request's first ``keep_first`` tokens visible for ever;
+    * ordinary softmax, then an element-wise output gate ``sigmoid(wg x)`` (``gated``) ahead of ``wo``.
+
+    All four projections of the input are one stacked product; what follows it (biases, norms,
+    the cache write, the gate's sigmoid) is one kernel; the gate is applied where the attention
+    kernel writes its result."""
+
+    graph_safe = True
+
+    def __init__(self, env: BuildEnv, *, dim: int, n_heads: int, n_kv_heads: int, head_dim: int,
+                 v_head_dim: Optional[int] = None, scale: float, window: Optional[int] = None, keep_first: int = 0,
+                 qkv_bias: bool = False, qk_norm: bool = False, norm_eps: float = 1e-6,
+                 distance_bias: bool = False, bias_rows: Optional[int] = None, bias_far: float = 0.0,
+                 gated: bool = False):
+        if n_heads % n_kv_heads != 0:
+            raise ValueError(f"n_heads ({n_heads}) must be a multiple of n_kv_heads ({n_kv_heads})")
+        if keep_first and window is None:
+            raise ValueError("keep_first goes with a window")
+        self.env = env
+        self.dim, self.n_heads, self.n_kv_heads = int(dim), int(n_heads), int(n_kv_heads)
+        self.head_dim = int(head_dim)
+        self.v_head_dim = int(v_head_dim if v_head_dim is not None else head_dim)
+        self.scale = float(scale)
+        self.window = None if window is None else int(window)
+        self.keep_first = int(keep_first)
+        self.qkv_bias, self.qk_norm, self.gated = bool(qkv_bias), bool(qk_norm), bool(gated)
+        self.norm_eps = float(norm_eps)
+        self.has_bias = bool(distance_bias)
+        self.bias_rows, self.bias_far = (None if bias_rows is None else int(bias_rows)), float(bias_far)
+        self.n_q = self.n_heads * self.head_dim
+        self.n_k = self.n_kv_heads * self.head_dim
+        self.n_v = self.n_kv_heads * self.v_head_dim
+        self.n_g = self.n_heads * self.v_head_dim if self.gated else 0
+        env.ops.check_attention_sizes(self.n_heads, self.n_kv_heads, self.head_dim, env.dtype, v_head_dim=self.v_head_dim)
+        self.buckets: Optional[torch.Tensor] = None
+        self.w_in: Optional[torch.Tensor] = None
+        self.b_in: Optional[torch.Tensor] = None
+        self.q_norm_w: Optional[torch.Tensor] = None
+        self.k_norm_w: Optional[torch.Tensor] = None
+        self.distance_bias: Optional[torch.Tensor] = None
+        self.wo: Optional[torch.Tensor] = None
+
+    def cache_need(self) -> CacheNeed:
+        if self.window is None:
+            return CacheNeed("full", self.n_kv_heads, self.head_dim, None, self.v_head_dim)
+        return CacheNeed("window", self.n_kv_heads, self.head_dim, self.window, self.v_head_dim, self.keep_first)
+
+    def expected_tensors(self) -> Dict[str, ExpectedTensor]:
+        out = {
+            "wq.weight": ExpectedTensor((self.n_q, self.dim)),
+            "wk.weight": ExpectedTensor((self.n_k, self.dim)),
+            "wv.weight": ExpectedTensor((self.n_v, self.dim)),
+            "wo.weight": ExpectedTensor((self.dim, self.n_heads * self.v_head_dim)),
+        }
+        if self.qkv_bias:
+            out.update({"wq.bias": ExpectedTensor((self.n_q,)), "wk.bias": ExpectedTensor((self.n_k,)),
+                        "wv.bias": ExpectedTensor((self.n_v,))})
+        if self.qk_norm:
+            out.update({"q_norm.weight": ExpectedTensor((self.n_q,)), "k_norm.weight": ExpectedTensor((self.n_k,))})
+        if self.has_bias:
+            out["distance_bias"] = ExpectedTensor((-1 if self.bias_rows is None else self.bias_rows, self.n_heads))
+        if self.gated:
+            out["wg.weight"] = ExpectedTensor((self.n_g, self.dim))
+        return out
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        f32 = dict(device=self.env.device, dtype=torch.float32)
+        names = ["wq.weight", "wk.weight", "wv.weight"] + (["wg.weight"] if self.gated else [])
+        self.w_in = torch.cat([as_compute(tensors[n], self.env) for n in names])       # rows [wq; wk; wv; wg]
+        if self.qkv_bias:
+            parts = [tensors[n].to(**f32) for n in ("wq.bias", "wk.bias", "wv.bias")]
+            parts.append(torch.zeros(self.n_g, **f32))
+            self.b_in = torch.cat(parts).contiguous()
+        if self.qk_norm:
+            self.q_norm_w = tensors["q_norm.weight"].to(**f32).contiguous()
+            self.k_norm_w = tensors["k_norm.weight"].to(**f32).contiguous()
+        if self.has_bias:
+            self.distance_bias = tensors["distance_bias"].to(**f32).contiguous()
+            self.buckets = distance_buckets(self.distance_bias.shape[0], self.bias_far, self.env.max_positions).to(self.env.device)
+        self.wo = as_compute(tensors["wo.weight"], self.env)
+
+    def forward(self, x: torch.Tensor, ctx, cache) -> PendingProduct:
+        ops = self.env.ops
+        proj = ops.linear(x, self.w_in, partials_ok=True)
+        q, gate = ops.project_and_store(
+            proj, n_q=self.n_q, n_k=self.n_k, n_v=self.n_v, n_extra=self.n_g, bias=self.b_in,
+            q_norm=self.q_norm_w, k_norm=self.k_norm_w, eps=self.norm_eps,
+            k_pages=cache.k_pages if cache.writes else None, v_pages=cache.v_pages if cache.writes else None,
+            slot_mapping=cache.slot_mapping, page_size=cache.page_size, out_dtype=self.env.dtype)
+        o = ops.paged_attention(
+            q.view(-1, self.n_heads, self.head_dim), cache.k_pages, cache.v_pages, cache.block_table, ctx.q_start,
+            ctx.kv_len, n_seqs=ctx.n_seqs, max_q_len=ctx.max_q_len, max_kv_len=ctx.max_kv_len, scale=self.scale,
+            window=self.window, page_size=cache.page_size, keep_first=self.keep_first,
+            distance_bias=self.distance_bias, distance_buckets=self.buckets, gate=gate, impl="general")
+        return PendingProduct(o.view(o.shape[0], self.n_heads * self.v_head_dim), self.wo)

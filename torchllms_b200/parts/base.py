@@ -48,20 +48,45 @@ class CacheNeed:
     """Paged key/value storage a mixer wants for every token of a request.
 
     ``kind`` is ``"full"`` (all keys stay) or ``"window"`` (only the last
-    ``window`` keys are ever read, so older pages may be given back).  Runs
-    with equal needs share one group of pages and one block table.
+    ``window`` keys are ever read, so older pages may be given back; with
+    ``keep_first`` the first so many tokens of a request are read for ever and
+    their pages stay).  ``v_head_dim`` is the size of a stored value when it
+    differs from a key's; 0 means that nothing but keys is stored (a mixer
+    that derives keys and values from one stored vector).  Runs with equal
+    needs share one group of pages and one block table.
     """
 
     kind: str
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    v_head_dim: Optional[int] = None
+    keep_first: int = 0
 
     def __post_init__(self):
         if self.kind not in ("full", "window"):
             raise ValueError(f"cache kind must be 'full' or 'window', got {self.kind!r}")
         if (self.kind == "window") != (self.window is not None):
             raise ValueError("a window size goes with kind 'window' and only with it")
+        if self.keep_first < 0 or (self.keep_first and self.kind != "window"):
+            raise ValueError("keep_first is a count of tokens and goes with kind 'window' only")
+        if self.v_head_dim is not None and self.v_head_dim == self.head_dim:
+            object.__setattr__(self, "v_head_dim", None)      # one spelling for equal needs
+
+    @property
+    def value_dim(self) -> int:
+        """Elements of one stored value (0: none are stored)."""
+        return self.head_dim if self.v_head_dim is None else self.v_head_dim
+
+    def covering(self, other: "CacheNeed") -> "CacheNeed":
+        """The need that keeps what both this one and ``other`` (a run that reads this run's cache
+        through a mask of its own) will read."""
+        if (other.n_kv_heads, other.head_dim, other.value_dim) != (self.n_kv_heads, self.head_dim, self.value_dim):
+            raise ValueError("a run can read another run's cache only if both store the same vectors")
+        if self.kind == "full" or other.kind == "full":
+            return CacheNeed("full", self.n_kv_heads, self.head_dim, None, self.v_head_dim, 0)
+        return CacheNeed("window", self.n_kv_heads, self.head_dim, max(self.window, other.window), self.v_head_dim,
+                         max(self.keep_first, other.keep_first))
 
 
 @dataclass(frozen=True)
@@ -191,13 +216,18 @@ class Residual:
     split-K product, which the norm kernel adds up as well, or a product not yet
     taken (:class:`~torchllms_b200.kernels.lazy.PendingProduct`), which the norm may
     hand to a kernel that adds it to ``h`` in its own epilogue.
+
+    ``rows`` is the stream as the activation dtype holds it, when the kernel that last wrote
+    ``h`` left such a copy (a block whose sublayers read the stream itself, without a norm in
+    front, takes its input from there); whoever changes ``h`` afterwards sets it to ``None``.
     """
 
-    __slots__ = ("h", "delta")
+    __slots__ = ("h", "delta", "rows")
 
-    def __init__(self, h: torch.Tensor, delta: Optional[torch.Tensor] = None):
+    def __init__(self, h: torch.Tensor, delta: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None):
         self.h = h
         self.delta = delta
+        self.rows = rows
 
 
 # --------------------------------------------------------------------------- registries

@@ -1,4 +1,6 @@
-"""Pre-norm residual block.
+"""The arrangements of a layer: where the norms sit and how the residual is carried.
+
+Pre-norm residual block.
 
 Reference: ``TransformerBlock.forward`` (torchllms/models/networks.py:635-644):
 ``h = x + mixer(norm1(x)); out = h + ffn(norm2(h))``.  The sums are left pending
@@ -7,7 +9,7 @@ on the residual so the following norm adds them in 32-bit in the same pass.
 
 from __future__ import annotations
 
-from typing import Dict, Mapping
+from typing import Dict, Mapping, Optional
 
 import torch
 
@@ -61,3 +63,56 @@ class PreNormBlock(Block):
         if norm.can_defer and reader.takes_row_scaled:
             return norm.forward(residual, deferred_ok=True)
         return norm.forward(residual)
+
+
+@register_block("outnorm")
+class OutputNormBlock(Block):
+    """The norm sits on each sublayer's output and nowhere else: ``x += norm1(mixer(x))``, then
+    ``x += norm2(ff(x))``; both sublayers read the stream itself.  A layer may have no feed-forward
+    (``feed_forward=None``), in which case it has no second norm either.
+
+    The sum is taken by the norm's own kernel (``Norm.fold_normed``), which also leaves the new
+    stream in the activation dtype for the next reader, so nothing is pending between sublayers."""
+
+    def __init__(self, env: BuildEnv, *, mixer: PartSpec, feed_forward: Optional[PartSpec],
+                 mixer_norm: PartSpec, ffn_norm: Optional[PartSpec],
+                 mixer_prefix: str, ffn_prefix: str, mixer_norm_prefix: str, ffn_norm_prefix: str):
+        self.env = env
+        self.mixer = MIXERS.build(mixer, env)
+        self.mixer_norm = NORMS.build(mixer_norm, env)
+        self.feed_forward = None if feed_forward is None else FEED_FORWARDS.build(feed_forward, env)
+        self.ffn_norm = None if feed_forward is None else NORMS.build(ffn_norm, env)
+        self._subparts = [(mixer_prefix, self.mixer), (mixer_norm_prefix, self.mixer_norm)]
+        if self.feed_forward is not None:
+            self._subparts += [(ffn_prefix, self.feed_forward), (ffn_norm_prefix, self.ffn_norm)]
+        self.graph_safe = all(sub.graph_safe for _p, sub in self._subparts)
+
+    def cache_need(self):
+        return self.mixer.cache_need()
+
+    def state_need(self):
+        return self.mixer.state_need()
+
+    def expected_tensors(self) -> Dict[str, ExpectedTensor]:
+        out: Dict[str, ExpectedTensor] = {}
+        for prefix, sub in self._subparts:
+            for name, e in sub.expected_tensors().items():
+                out[f"{prefix}.{name}"] = e
+        return out
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        for prefix, sub in self._subparts:
+            sub.load({name: tensors[f"{prefix}.{name}"] for name in sub.expected_tensors()})
+
+    def _input(self, residual: Residual) -> torch.Tensor:
+        """The stream as a sublayer reads it: in the activation dtype."""
+        if residual.delta is not None:
+            raise RuntimeError("an output-norm block cannot follow a block that leaves its sum pending")
+        if residual.rows is None:
+            residual.rows = self.env.ops.stream_rows(residual.h, self.env.dtype)
+        return residual.rows
+
+    def forward(self, residual: Residual, ctx, cache) -> None:
+        self.mixer_norm.fold_normed(residual, self.mixer.forward(self._input(residual), ctx, cache))
+        if self.feed_forward is not None:
+            self.ffn_norm.fold_normed(residual, self.feed_forward.forward(self._input(residual), ctx))

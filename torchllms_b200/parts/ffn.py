@@ -44,3 +44,39 @@ class SwiGLU(FeedForward):
         # kernel can (decode steps), else product [T, 2 * hidden] + SwiGLU kernel
         # the down projection is left to the norm that follows (see PendingProduct)
         return PendingProduct(ops.linear_swiglu(x, self.w13), self.w2)
+
+
+@register_feed_forward("clamped_glu")
+class ClampedGLU(FeedForward):
+    """Dense gated feed-forward with bounded branches:
+    ``g = min(gate x, limit)``, ``u = clamp(up x, -limit, limit)``,
+    ``y = g * sigmoid(alpha * g) * (u + up_offset)``, output ``down y``.  Weights ``gate.weight`` and
+    ``up.weight`` are ``[hidden, dim]``, ``down.weight`` is ``[dim, hidden]``; gate and up are
+    stacked so that one product yields both."""
+
+    graph_safe = True
+
+    def __init__(self, env: BuildEnv, *, dim: int, hidden: int, limit: float, alpha: float = 1.702,
+                 up_offset: float = 1.0):
+        self.env = env
+        self.dim, self.hidden = int(dim), int(hidden)
+        self.limit, self.alpha, self.up_offset = float(limit), float(alpha), float(up_offset)
+        if not self.limit > 0:
+            raise ValueError(f"the bound of a clamped feed-forward must be positive, got {limit}")
+        self.w_gate_up: Optional[torch.Tensor] = None
+        self.w_down: Optional[torch.Tensor] = None
+
+    def expected_tensors(self) -> Dict[str, ExpectedTensor]:
+        return {
+            "gate.weight": ExpectedTensor((self.hidden, self.dim)),
+            "up.weight": ExpectedTensor((self.hidden, self.dim)),
+            "down.weight": ExpectedTensor((self.dim, self.hidden)),
+        }
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        self.w_gate_up = torch.cat([as_compute(tensors["gate.weight"], self.env), as_compute(tensors["up.weight"], self.env)])
+        self.w_down = as_compute(tensors["down.weight"], self.env)
+
+    def forward(self, x: torch.Tensor, ctx) -> PendingProduct:
+        y = self.env.ops.linear_glu(x, self.w_gate_up, limit=self.limit, alpha=self.alpha, up_offset=self.up_offset)
+        return PendingProduct(y, self.w_down)       # the down projection is left to the norm that follows

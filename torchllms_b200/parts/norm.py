@@ -33,10 +33,12 @@ class RMSNorm(Norm):
     graph_safe = True
     can_defer = True
 
-    def __init__(self, env: BuildEnv, *, dim: int, eps: float):
+    def __init__(self, env: BuildEnv, *, dim: int, eps: float, offset: float = 0.0):
+        """``offset``: what is added to the stored weight (1 for a weight that is kept around zero)."""
         self.env = env
         self.dim = int(dim)
         self.eps = float(eps)
+        self.offset = float(offset)
         self.weight: Optional[torch.Tensor] = None
 
     def expected_tensors(self) -> Dict[str, ExpectedTensor]:
@@ -44,7 +46,7 @@ class RMSNorm(Norm):
 
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
         # Kept in 32-bit whatever the activation dtype: the kernel multiplies in 32-bit.
-        self.weight = tensors["weight"].to(device=self.env.device, dtype=torch.float32).contiguous()
+        self.weight = (tensors["weight"].to(device=self.env.device, dtype=torch.float32) + self.offset).contiguous()
 
     def forward(self, residual: Residual, rows: Optional[torch.Tensor] = None, deferred_ok: bool = False):
         ops = self.env.ops
@@ -54,6 +56,7 @@ class RMSNorm(Norm):
         if deferred and isinstance(delta, PendingProduct) and ops.can_fuse_residual(delta, residual.h):
             out = ops.linear_residual_norm(delta, residual.h, self.weight, self.eps)   # h += product, in the product's kernel
             residual.delta = None
+            residual.rows = None
             return out
         if deferred:
             out = ops.rmsnorm(residual.h, delta, self.weight, self.eps, out_dtype=self.env.dtype, deferred=True)
@@ -61,4 +64,13 @@ class RMSNorm(Norm):
             out = ops.rmsnorm(residual.h, delta, self.weight, self.eps, out_dtype=self.env.dtype, rows=rows)
         if rows is None:
             residual.delta = None  # the kernel wrote h + delta back into the stream
+            residual.rows = None
         return out
+
+    def fold_normed(self, residual: Residual, delta) -> None:
+        """The norm on a sublayer's *output*: ``h += norm(delta)`` in 32-bit, in one kernel that also
+        leaves the new stream in the activation dtype (``residual.rows``) for the sublayer that
+        reads it next.  ``delta`` is a tensor, float32 partial sums or a
+        :class:`~torchllms_b200.kernels.lazy.PendingProduct`."""
+        residual.rows = self.env.ops.norm_add(residual.h, delta, self.weight, self.eps, out_dtype=self.env.dtype)
+        residual.delta = None

@@ -72,6 +72,8 @@ class ModelSpec:
     final_norm_prefix: str           # prefix of the final norm's tensors
     head_tensor: str                 # name of the [vocab, dim] output matrix
     tie_head: bool = False           # the head is the embedding table; head_tensor is absent
+    embedding_scale: float = 1.0     # the rows of the table enter the stream multiplied by this
+    position_tensor: Optional[str] = None   # name of a learned [max_positions, dim] table added to the embedding
 
     def __post_init__(self):
         n = len(self.layers)

@@ -67,6 +67,8 @@ class LazyTensor:
 
 @dataclass(frozen=True)
 class ExpectedTensor:
+    # a size of -1 stands for "whatever the stored tensor has there" (a table whose number of rows
+    # no configuration carries); the part reads the size when it is handed the tensor
     shape: Tuple[int, ...]
     # "float": any floating dtype is accepted and handed over as stored;
     # "int": an integer table, handed over as int32.
@@ -79,6 +81,10 @@ def source_tensors(source: TensorSource) -> Dict[str, LazyTensor]:
             for name in source.names()}
 
 
+def shape_fits(found: Tuple[int, ...], expected: Tuple[int, ...]) -> bool:
+    return len(found) == len(expected) and all(e == -1 or f == e for f, e in zip(found, expected))
+
+
 def check_tensors(where: str, expected: Mapping[str, ExpectedTensor],
                   found: Mapping[str, LazyTensor], ignorable: Iterable[str] = ()) -> None:
     """Raise one :class:`WeightError` for every mismatch between the two sets."""
@@ -86,7 +92,7 @@ def check_tensors(where: str, expected: Mapping[str, ExpectedTensor],
     missing = [n for n in expected if n not in found]
     unexpected = [n for n in found if n not in expected and n not in ignorable]
     wrong = [(n, tuple(e.shape), tuple(found[n].shape)) for n, e in expected.items()
-             if n in found and tuple(found[n].shape) != tuple(e.shape)]
+             if n in found and not shape_fits(tuple(found[n].shape), tuple(e.shape))]
     other = []
     for n, e in expected.items():
         if n in found and n not in [w[0] for w in wrong]:
