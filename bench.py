@@ -261,6 +261,110 @@ def serving_workload(args, peaks):
     })
 
 
+# ---------------------------------------------------------------------- a design beside its closest model
+DESIGN_SIZES = {
+    # name -> width, heads, kv heads, head size, latent rank, feed-forward width, layers, windows
+    "w2048": dict(dim=2048, heads=16, kv_heads=4, head_dim=128, rank=128, ff=8192, layers=4, window=1024, keep_first=4),
+    "w4096": dict(dim=4096, heads=32, kv_heads=8, head_dim=128, rank=128, ff=14336, layers=4, window=1024, keep_first=4),
+}
+
+
+def design_workload(args, peaks):
+    """Nagolix beside the Llama decoder at equal sizes (random weights, bfloat16): for every size
+    of ``DESIGN_SIZES`` the prefill of one 2,048-token prompt and decode steps at batch 8 behind
+    2,048-token prompts, timed with CUDA events on the step function, and where each model's time goes
+    (per kernel-library call, from ``ops.profile()``).  Nagolix layers alternate latent attention,
+    attention, latent attention reading the first one's latents, attention."""
+    import torch
+    from torchllms_b200.engine.step import StepEntry
+    from torchllms_b200.inference import LLM
+    from torchllms_b200.models.llama_config import LlamaConfig, RopeScaling
+    from torchllms_b200.models.nagolix import LayerConfig, MixerConfig, MlpConfig, NagolixConfig
+
+    vocab, prompt_len, batch = 32000, PROMPT_LEN, args.batch
+    steps, warmup = min(args.steps, 64), max(args.warmup, 3)
+    max_len = prompt_len + warmup + steps + 64
+    gen = torch.Generator().manual_seed(7)
+    out = {}
+    for name, z in DESIGN_SIZES.items():
+        hd = z["head_dim"]
+        att = MixerConfig("attention", z["heads"], hd, hd, hd ** -0.5, z["window"], z["keep_first"], z["kv_heads"], 4096.0)
+        lat = MixerConfig("latent_attention", z["heads"], hd, hd, hd ** -0.5, z["window"], kv_rank=z["rank"])
+        lat2 = MixerConfig("latent_attention", z["heads"], hd, hd, hd ** -0.5, z["window"], kv_rank=z["rank"], kv_from=0)
+        mlp = MlpConfig("dense", z["ff"], 7.0)
+        kinds = [lat, att, lat2, att]
+        configs = {
+            "nagolix": NagolixConfig("Nagolix", vocab, z["dim"], max_len, 1e-6, 1.0,
+                                     tuple(LayerConfig(kinds[i % 4], mlp) for i in range(z["layers"]))),
+            "llama": LlamaConfig(architecture="LlamaForCausalLM", n_layers=z["layers"], dim=z["dim"], n_heads=z["heads"],
+                                 n_kv_heads=z["kv_heads"], head_dim=hd, ffn_hidden=z["ff"], vocab_size=vocab, norm_eps=1e-5,
+                                 rope_theta=500000.0, rope_scaling=RopeScaling(), tie_word_embeddings=True, max_seq_len=max_len),
+        }
+        out[name] = {}
+        for model, cfg in configs.items():
+            llm = LLM(config=cfg, random_seed=0, precision="bfloat16", max_len=max_len, max_bsz=batch,
+                      max_num_batched_tokens=prompt_len, page_size=16)
+            engine, ops = llm.engine, llm.model.ops
+
+            def prefill(profile=False):
+                h = engine.claim()
+                toks = torch.randint(0, vocab, (prompt_len,), generator=gen).tolist()
+                torch.cuda.synchronize()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                engine.step([StepEntry(h, toks, [prompt_len - 1])])
+                b.record()
+                torch.cuda.synchronize()
+                engine.release(h)
+                return a.elapsed_time(b)
+
+            for _ in range(3):
+                prefill()
+            pre_ms = sorted(prefill() for _ in range(5))[2]
+            graphs, engine.use_graphs = engine.use_graphs, False          # a profile needs the calls themselves
+            with ops.profile() as pre_prof:
+                prefill()
+            engine.use_graphs = graphs
+            handles = [engine.claim() for _ in range(batch)]
+            for h in handles:
+                engine.step([StepEntry(h, torch.randint(0, vocab, (prompt_len,), generator=gen).tolist(), [])])
+            feed = torch.randint(0, vocab, (warmup + steps + 1, batch), generator=gen).tolist()
+            for i in range(warmup):
+                engine.step([StepEntry(h, [t]) for h, t in zip(handles, feed[i])])
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            launches0 = ops.launches
+            a.record()
+            for i in range(warmup, warmup + steps):
+                engine.step([StepEntry(h, [t]) for h, t in zip(handles, feed[i])])
+            b.record()
+            torch.cuda.synchronize()
+            dec_ms = a.elapsed_time(b) / steps
+            launches = ops.launches - launches0
+            graphs, engine.use_graphs = engine.use_graphs, False          # the profile needs the calls themselves
+            with ops.profile() as dec_prof:
+                engine.step([StepEntry(h, [t]) for h, t in zip(handles, feed[-1])])
+            engine.use_graphs = graphs
+            for h in handles:
+                engine.release(h)
+            ops.check_status()
+            out[name][model] = {
+                "prefill_tokens_per_s": round(prompt_len / pre_ms * 1e3, 1), "prefill_ms": round(pre_ms, 3),
+                "decode_tokens_per_s": round(batch / dec_ms * 1e3, 1), "decode_ms_per_step": round(dec_ms, 4),
+                "weight_bytes": llm.model.weight_bytes(), "cache_bytes": engine.cache.bytes(),
+                "decode_weight_roofline_frac": round(llm.model.weight_bytes() / (dec_ms / 1e3) / (peaks["hbm_gbs"] * 1e9), 4),
+                "gpu_launches_per_decode_step": launches / steps,
+                "prefill_profile_ms": {k: [v[0], round(v[1], 3)] for k, v in sorted(pre_prof.items())},
+                "decode_profile_ms": {k: [v[0], round(v[1], 4)] for k, v in sorted(dec_prof.items())},
+            }
+            del llm, engine
+            torch.cuda.empty_cache()
+    return {"metric": "Nagolix beside Llama at equal sizes: prefill and decode tokens/s", "unit": "tokens/s", "n_gpus": 1,
+            "dtype": "bf16", "data": "synthetic (uniform random token ids, random weights)",
+            "config": {"prompt_len": prompt_len, "batch": batch, "decode_steps": steps, "warmup": warmup, "vocab": vocab,
+                       "sizes": DESIGN_SIZES}, "sizes": out, "peaks": peaks["source"]}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -270,8 +374,9 @@ def main():
     ap.add_argument("--layers", type=int, default=SHAPE_8B["n_layers"], help="fewer layers than the shape has (named in config)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--skip-points", action="store_true", help="only the headline batch and the prefill")
-    ap.add_argument("--workload", default="decode_8b", choices=["decode_8b"] + sorted(SERVE),
-                    help="decode_8b: the headline (default); serve_1b, long_3b: whole serving runs through LLM.generate")
+    ap.add_argument("--workload", default="decode_8b", choices=["decode_8b", "design_nagolix"] + sorted(SERVE),
+                    help="decode_8b: the headline (default); serve_1b, long_3b: whole serving runs through LLM.generate; "
+                         "design_nagolix: the Nagolix design beside the Llama decoder at equal sizes")
     ap.add_argument("--context-len", type=int, default=PROMPT_LEN,
                     help="prompt length of the decode measurements (the headline is 2,048; the prefill figure stays at 2,048)")
     ap.add_argument("--long-contexts", type=lambda t: [int(x) for x in t.split(",") if x], default=[8192, 32768],
@@ -288,6 +393,9 @@ def main():
         return 2
     if args.impl == "reference":
         return reference_arm(args)
+    if args.workload == "design_nagolix":
+        print(json.dumps(design_workload(args, load_peaks())))
+        return 0
     if args.workload != "decode_8b":
         print(json.dumps(serving_workload(args, load_peaks())))
         return 0

@@ -566,7 +566,7 @@ def test_prefill_attention_on_random_shapes(ops, seed):
 def test_attention_refuses_sizes_it_cannot_do(ops):
     from torchllms_b200.kernels.native import KernelError
     with pytest.raises(KernelError):
-        ops.check_attention_sizes(4, 2, 24, torch.float32)     # head_dim no multiple of 16
+        ops.check_attention_sizes(4, 2, 24, torch.float32, v_head_dim=264)     # values too wide
     with pytest.raises(KernelError):
         ops.check_attention_sizes(4, 3, 32, torch.float32)     # heads no multiple of kv heads
     with pytest.raises(KernelError):

@@ -15,6 +15,13 @@
 //              (max, sum, accumulator) are merged through shared memory.  The key range may also be
 //              cut over several CTAs; those partials go to a float32 workspace and are combined
 //              by merge_partials_kernel (same layout as the general kernel's).
+//
+// The extended form (template flag EXT, a separate entry point) also takes what the general
+// kernel's options describe: keys and values of sizes of their own (multiples of 8 up to the
+// instantiated size, the tiles' spare columns zero-filled), one stored vector read as key and as
+// value (the value tile is the key tile), a window that keeps a request's first keys visible (they
+// are walked as tiles of their own ahead of the window's), a bias by bucketed distance added to the
+// scaled score, and an output gate per head or per element.
 #include "common.cuh"
 #include <limits.h>
 #include <math.h>
@@ -47,6 +54,15 @@ struct MmaParams {
     int window;
     int n_splits;
     float scale_log2;           // scale * log2(e)
+    // ---- the extended form only
+    int hd, dv;                 // true sizes of a key and of a value
+    int shared_kv;              // 1: v_pages is k_pages, a tile is loaded once
+    int keep_first;
+    const float* rel;           // [rows, n_heads] or null
+    const int* bucket;          // [n_bucket]
+    int n_bucket;
+    const __nv_bfloat16* gate;
+    int gate_mode;              // 0: none, 1: [T, n_heads], 2: [T, n_heads * dv]
 };
 
 __device__ __forceinline__ unsigned smem_addr(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -80,8 +96,9 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
     return *reinterpret_cast<unsigned*>(&v);
 }
 
-template <int HD, bool KEY_SPLIT>
+template <int HD, bool KEY_SPLIT, bool EXT>
 __global__ void __launch_bounds__(NT, KEY_SPLIT ? 4 : 2) attention_mma_kernel(const MmaParams p) {
+    const int hd = EXT ? p.hd : HD, dv = EXT ? p.dv : HD;
     constexpr int PITCH = HD + 8;                 // bf16 elements per shared-memory row
     constexpr int QROWS = KEY_SPLIT ? 16 : 16 * NW;
     constexpr int KG = KEY_SPLIT ? 1 : 4;         // 16-key groups of a tile that one warp handles
@@ -115,9 +132,9 @@ __global__ void __launch_bounds__(NT, KEY_SPLIT ? 4 : 2) attention_mma_kernel(co
         const int rr = r & 15;
         const int tok = tok0 + wtile * p.tpw + rr / ng;
         uint4 v = make_uint4(0u, 0u, 0u, 0u);
-        if (rr < p.tpw * ng && tok < ql) {
+        if (rr < p.tpw * ng && tok < ql && part * 8 < hd) {
             const int head = kvh * p.group + g0 + rr % ng;
-            v = *reinterpret_cast<const uint4*>(p.q + ((size_t)(qs + tok) * p.n_heads + head) * HD + part * 8);
+            v = *reinterpret_cast<const uint4*>(p.q + ((size_t)(qs + tok) * p.n_heads + head) * hd + part * 8);
         }
         *reinterpret_cast<uint4*>(Qs + r * PITCH + part * 8) = v;
     }
@@ -125,17 +142,23 @@ __global__ void __launch_bounds__(NT, KEY_SPLIT ? 4 : 2) attention_mma_kernel(co
     // ---- which keys this CTA walks
     const int cta_tok_hi = min(ql, tok0 + tokens_per_cta);              // exclusive
     const int qpos_base = kl - ql;
-    int k_lo = p.window > 0 ? max(0, qpos_base + tok0 - p.window + 1) : 0;
-    int k_hi = qpos_base + cta_tok_hi;                                   // last query's position + 1
+    // The window's keys start at win_lo; ahead of them, in tiles of their own, the kept first keys
+    // that the window of the CTA's earliest query has passed (none unless EXT).  Tile i of the walk
+    // starts at key tile_k0(i) and ends before tile_hi(i).
+    const int win_lo = p.window > 0 ? max(0, qpos_base + tok0 - p.window + 1) : 0;
+    const int win_hi = qpos_base + cta_tok_hi;                           // last query's position + 1
+    const int n_kept = EXT ? min(p.keep_first, win_lo) : 0;
+    const int kept_tiles = (n_kept + BN - 1) / BN;
+    int t_lo = 0, t_hi = kept_tiles + (win_hi > win_lo ? (win_hi - win_lo + BN - 1) / BN : 0);
     if (p.n_splits > 1) {
         // every request cuts its own visible keys evenly, in whole tiles, so the launch shape
         // depends on the batch size only and not on how long the requests have grown
-        const int len = max(k_hi - k_lo, 0);
-        const int chunk = ((len + p.n_splits - 1) / p.n_splits + BN - 1) / BN * BN;
-        const int lo = k_lo + split * chunk;
-        k_hi = min(k_hi, lo + chunk);
-        k_lo = lo;
+        const int per = (t_hi + p.n_splits - 1) / p.n_splits;
+        t_lo = split * per;
+        t_hi = min(t_hi, t_lo + per);
     }
+    auto tile_k0 = [&](int i) { return i < kept_tiles ? i * BN : win_lo + (i - kept_tiles) * BN; };
+    auto tile_hi = [&](int i) { return i < kept_tiles ? n_kept : win_hi; };
 
     // rows of this thread: g and g + 8 of the warp's tile
     const int wtile = KEY_SPLIT ? 0 : warp;
@@ -157,16 +180,20 @@ __global__ void __launch_bounds__(NT, KEY_SPLIT ? 4 : 2) attention_mma_kernel(co
     const int ld_key0 = tid / CHUNKS;
     constexpr int LD_STEP = NT / CHUNKS;          // keys between two chunks of one thread
     constexpr int LD_ITERS = BN / LD_STEP;
-    const size_t head_off = (size_t)kvh * p.page_size * HD + ld_part;
-    const size_t page_stride = (size_t)p.n_kv_heads * p.page_size * HD;
-    auto load_tile = [&](int stage, int k0) {
+    const size_t page_stride_k = (size_t)p.n_kv_heads * p.page_size * hd;
+    const size_t page_stride_v = (size_t)p.n_kv_heads * p.page_size * dv;
+    const size_t head_off_k = (size_t)kvh * p.page_size * hd + ld_part;
+    const size_t head_off_v = (size_t)kvh * p.page_size * dv + ld_part;
+    const bool k_real = ld_part < hd, v_real = ld_part < dv && !(EXT && p.shared_kv);
+    auto load_tile = [&](int stage, int k0, int k_end) {
         __nv_bfloat16* kd = Ks + stage * BN * PITCH + ld_part;
         __nv_bfloat16* vd = Vs + stage * BN * PITCH + ld_part;
 #pragma unroll
         for (int i = 0; i < LD_ITERS; ++i) {
             const int j = ld_key0 + i * LD_STEP;
             const int kpos = k0 + j;
-            if (kpos < k_hi) {   // kpos >= k_lo always: pages behind a window may be gone and are never touched
+            bool k_done = false, v_done = false;
+            if (kpos < k_end) {   // kpos >= the walk's first key always: pages behind a window may be gone and are never touched
                 int blk, slot;
                 if (p.page_shift >= 0) {
                     blk = kpos >> p.page_shift;
@@ -175,13 +202,18 @@ __global__ void __launch_bounds__(NT, KEY_SPLIT ? 4 : 2) attention_mma_kernel(co
                     blk = kpos / p.page_size;
                     slot = kpos - blk * p.page_size;
                 }
-                const size_t off = (size_t)(tl_check_page(table[blk]) ? table[blk] : 0) * page_stride + head_off + (size_t)slot * HD;
-                cp_async16(kd + j * PITCH, p.k_pages + off);      // (debug builds: a bad page is reported, page 0 read in its place)
-                cp_async16(vd + j * PITCH, p.v_pages + off);
-            } else {
-                *reinterpret_cast<uint4*>(kd + j * PITCH) = make_uint4(0u, 0u, 0u, 0u);
-                *reinterpret_cast<uint4*>(vd + j * PITCH) = make_uint4(0u, 0u, 0u, 0u);
+                const size_t page = (size_t)(tl_check_page(table[blk]) ? table[blk] : 0);   // (debug builds: a bad page is reported, page 0 read in its place)
+                if (k_real) {
+                    cp_async16(kd + j * PITCH, p.k_pages + page * page_stride_k + head_off_k + (size_t)slot * hd);
+                    k_done = true;
+                }
+                if (v_real) {
+                    cp_async16(vd + j * PITCH, p.v_pages + page * page_stride_v + head_off_v + (size_t)slot * dv);
+                    v_done = true;
+                }
             }
+            if (!k_done) *reinterpret_cast<uint4*>(kd + j * PITCH) = make_uint4(0u, 0u, 0u, 0u);
+            if (!v_done && !(EXT && p.shared_kv)) *reinterpret_cast<uint4*>(vd + j * PITCH) = make_uint4(0u, 0u, 0u, 0u);
         }
     };
 
@@ -191,8 +223,8 @@ __global__ void __launch_bounds__(NT, KEY_SPLIT ? 4 : 2) attention_mma_kernel(co
     for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     unsigned qf[KSTEPS][4];
 
-    const int n_tiles = k_hi > k_lo ? (k_hi - k_lo + BN - 1) / BN : 0;
-    if (n_tiles > 0) load_tile(0, k_lo);
+    const int n_tiles = max(t_hi - t_lo, 0);
+    if (n_tiles > 0) load_tile(0, tile_k0(t_lo), tile_hi(t_lo));
     cp_async_commit();
     __syncthreads();   // Qs is complete
 #pragma unroll
@@ -203,13 +235,13 @@ __global__ void __launch_bounds__(NT, KEY_SPLIT ? 4 : 2) attention_mma_kernel(co
     }
 
     for (int it = 0; it < n_tiles; ++it) {
-        const int k0 = k_lo + it * BN;
-        if (it + 1 < n_tiles) load_tile((it + 1) & 1, k0 + BN);
+        const int k0 = tile_k0(t_lo + it), k_hi = tile_hi(t_lo + it);
+        if (it + 1 < n_tiles) load_tile((it + 1) & 1, tile_k0(t_lo + it + 1), tile_hi(t_lo + it + 1));
         cp_async_commit();
         cp_async_wait<1>();
         __syncthreads();
         const __nv_bfloat16* kt = Ks + (it & 1) * BN * PITCH;
-        const __nv_bfloat16* vt = Vs + (it & 1) * BN * PITCH;
+        const __nv_bfloat16* vt = (EXT && p.shared_kv) ? kt : Vs + (it & 1) * BN * PITCH;
         const int key_off = KEY_SPLIT ? warp * 16 : 0;
         if (k0 + key_off <= warp_qmax) {     // else every key of this warp's share lies beyond its queries
             float s[2 * KG][4];
@@ -230,16 +262,40 @@ __global__ void __launch_bounds__(NT, KEY_SPLIT ? 4 : 2) attention_mma_kernel(co
             // ---- mask, streaming softmax (base 2; the scale is folded into the exponent)
             float mx[2] = {-INFINITY, -INFINITY};
             const int share_lo = k0 + key_off, share_hi = share_lo + 16 * KG;   // this warp's keys of the tile
+            const bool biased = EXT && p.rel != nullptr;
+            const float sl = biased ? 1.f : p.scale_log2;       // biased scores are put on the base-2 scale below
             const bool all_visible = share_hi <= k_hi && share_hi - 1 <= warp_qmin &&
                                      (p.window <= 0 || share_lo > warp_qmax - p.window);
-            if (!all_visible) {      // else every key counts for every row: no per-element tests
+            if (biased) {
+                // score * scale + rel[bucket[distance], head], on the base-2 scale; hidden keys get -inf
+                int head[2];
+#pragma unroll
+                for (int i = 0; i < 2; ++i) head[i] = kvh * p.group + g0 + (g + 8 * i) % ng;
 #pragma unroll
                 for (int nt = 0; nt < 2 * KG; ++nt) {
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
                         const int i = e >> 1;
                         const int kpos = share_lo + nt * 8 + 2 * t + (e & 1);
-                        const bool ok = kpos <= qpos[i] && kpos < k_hi && (p.window <= 0 || kpos > qpos[i] - p.window);
+                        const bool ok = kpos <= qpos[i] && kpos < k_hi &&
+                                        (p.window <= 0 || kpos > qpos[i] - p.window || kpos < p.keep_first);
+                        float v = -INFINITY;
+                        if (ok) {
+                            const int row = __ldg(p.bucket + min(qpos[i] - kpos, p.n_bucket - 1));
+                            v = fmaf(s[nt][e], p.scale_log2, __ldg(p.rel + (size_t)row * p.n_heads + head[i]) * LOG2E);
+                        }
+                        s[nt][e] = v;
+                    }
+                }
+            } else if (!all_visible) {      // else every key counts for every row: no per-element tests
+#pragma unroll
+                for (int nt = 0; nt < 2 * KG; ++nt) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int i = e >> 1;
+                        const int kpos = share_lo + nt * 8 + 2 * t + (e & 1);
+                        const bool ok = kpos <= qpos[i] && kpos < k_hi &&
+                                        (p.window <= 0 || kpos > qpos[i] - p.window || (EXT && kpos < p.keep_first));
                         if (!ok) s[nt][e] = -INFINITY;
                     }
                 }
@@ -253,7 +309,7 @@ __global__ void __launch_bounds__(NT, KEY_SPLIT ? 4 : 2) attention_mma_kernel(co
             for (int i = 0; i < 2; ++i) {
                 mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
                 mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
-                const float m_new = fmaxf(m[i], mx[i] * p.scale_log2);       // maxima live on the base-2 scale
+                const float m_new = fmaxf(m[i], mx[i] * sl);       // maxima live on the base-2 scale
                 m_safe[i] = (m_new == -INFINITY) ? 0.f : m_new;                // no key seen yet: keep exponents finite
                 alpha[i] = ex2(m[i] - m_safe[i]);
                 m[i] = m_new;
@@ -263,7 +319,7 @@ __global__ void __launch_bounds__(NT, KEY_SPLIT ? 4 : 2) attention_mma_kernel(co
             for (int nt = 0; nt < 2 * KG; ++nt) {
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    const float pv = ex2(fmaf(s[nt][e], p.scale_log2, -m_safe[e >> 1]));
+                    const float pv = ex2(fmaf(s[nt][e], sl, -m_safe[e >> 1]));
                     s[nt][e] = pv;
                     l[e >> 1] += pv;
                 }
@@ -321,11 +377,21 @@ __global__ void __launch_bounds__(NT, KEY_SPLIT ? 4 : 2) attention_mma_kernel(co
             const int rr = g + 8 * i;
             const int tok = qs + tok0 + warp * p.tpw + rr / ng;
             const int head = kvh * p.group + g0 + rr % ng;
-            __nv_bfloat16* dst = p.out + ((size_t)tok * p.n_heads + head) * HD;
-            const float inv = l[i] > 0.f ? 1.f / l[i] : 0.f;
+            const size_t row = (size_t)tok * p.n_heads + head;
+            __nv_bfloat16* dst = p.out + row * dv;
+            float inv = l[i] > 0.f ? 1.f / l[i] : 0.f;
+            if (EXT && p.gate_mode == 1) inv *= __bfloat162float(p.gate[row]);
 #pragma unroll
-            for (int nt = 0; nt < HD / 8; ++nt)
-                *reinterpret_cast<unsigned*>(dst + nt * 8 + 2 * t) = pack_bf16(o[nt][2 * i] * inv, o[nt][2 * i + 1] * inv);
+            for (int nt = 0; nt < HD / 8; ++nt) {
+                if (EXT && nt * 8 >= dv) break;
+                float a = o[nt][2 * i] * inv, c = o[nt][2 * i + 1] * inv;
+                if (EXT && p.gate_mode == 2) {
+                    const float2 gv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p.gate + row * dv + nt * 8 + 2 * t));
+                    a *= gv.x;
+                    c *= gv.y;
+                }
+                *reinterpret_cast<unsigned*>(dst + nt * 8 + 2 * t) = pack_bf16(a, c);
+            }
         }
         return;
     }
@@ -367,10 +433,14 @@ __global__ void __launch_bounds__(NT, KEY_SPLIT ? 4 : 2) attention_mma_kernel(co
         const int tok = qs + tok0 + rr / ng;
         const int head = kvh * p.group + g0 + rr % ng;
         const size_t row = (size_t)tok * p.n_heads + head;
+        if (EXT && d >= dv) continue;
         if (p.n_splits == 1) {
-            p.out[row * HD + d] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+            float v = den > 0.f ? num / den : 0.f;
+            if (EXT && p.gate_mode == 1) v *= __bfloat162float(p.gate[row]);
+            else if (EXT && p.gate_mode == 2) v *= __bfloat162float(p.gate[row * dv + d]);
+            p.out[row * dv + d] = __float2bfloat16_rn(v);
         } else {
-            p.part_o[(row * p.n_splits + split) * HD + d] = num;
+            p.part_o[(row * p.n_splits + split) * dv + d] = num;
             if (d == 0) {
                 p.part_ml[(row * p.n_splits + split) * 2] = (M == -INFINITY) ? -INFINITY : M * LN2;   // natural-log scale
                 p.part_ml[(row * p.n_splits + split) * 2 + 1] = den;
@@ -384,7 +454,8 @@ __global__ void __launch_bounds__(NT, KEY_SPLIT ? 4 : 2) attention_mma_kernel(co
 // memory, then every thread sums its head_dim lanes over the splits in order.
 constexpr int MERGE_MAX_SPLITS = 256;
 __global__ void merge_partials_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                      __nv_bfloat16* __restrict__ out, int n_splits, int head_dim) {
+                                      __nv_bfloat16* __restrict__ out, int n_splits, int head_dim,
+                                      const __nv_bfloat16* __restrict__ gate = nullptr, int gate_mode = 0) {
     __shared__ float wgt[MERGE_MAX_SPLITS];
     __shared__ float red[2];
     const size_t row = blockIdx.x;
@@ -409,7 +480,10 @@ __global__ void merge_partials_kernel(const float* __restrict__ part_o, const fl
     for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
         float num = 0.f;
         for (int i = 0; i < n_splits; ++i) num = fmaf(wgt[i], part_o[(row * n_splits + i) * head_dim + d], num);
-        out[row * head_dim + d] = __float2bfloat16_rn(num * inv);
+        float v = num * inv;
+        if (gate_mode == 1) v *= __bfloat162float(gate[row]);
+        else if (gate_mode == 2) v *= __bfloat162float(gate[row * head_dim + d]);
+        out[row * head_dim + d] = __float2bfloat16_rn(v);
     }
 }
 
@@ -417,8 +491,11 @@ struct Plan {
     int ng, n_gchunks, tpw, key_split, n_q_tiles, n_splits;
 };
 
-Plan make_plan(int n_seqs, int n_heads, int n_kv_heads, int max_q_len, int max_kv_len, int allow_split) {
+Plan make_plan(int n_seqs, int n_heads, int n_kv_heads, int max_q_len, int max_kv_len, int allow_split,
+               int window = 0, int keep_first = 0) {
     Plan pl;
+    // (the extended form tells its window: behind one, what a query tile sees does not grow with the context)
+    if (window > 0 && max_kv_len > (long long)window + keep_first + max_q_len) max_kv_len = window + keep_first + max_q_len;
     const int group = n_heads / n_kv_heads;
     pl.ng = group < 16 ? group : 16;
     pl.n_gchunks = (group + pl.ng - 1) / pl.ng;
@@ -448,14 +525,14 @@ Plan make_plan(int n_seqs, int n_heads, int n_kv_heads, int max_q_len, int max_k
     return pl;
 }
 
-template <int HD, bool KEY_SPLIT>
+template <int HD, bool KEY_SPLIT, bool EXT = false>
 int launch(const MmaParams& p, dim3 grid, cudaStream_t s) {
     constexpr int PITCH = HD + 8;
     constexpr int QROWS = KEY_SPLIT ? 16 : 16 * NW;
     size_t smem = (size_t)(QROWS + 4 * BN) * PITCH * sizeof(__nv_bfloat16);
     const size_t merge = KEY_SPLIT ? (size_t)(NW * 16 * (HD + 2)) * sizeof(float) : 0;
     if (merge > smem) smem = merge;
-    auto kern = attention_mma_kernel<HD, KEY_SPLIT>;
+    auto kern = attention_mma_kernel<HD, KEY_SPLIT, EXT>;
     static bool raised = false;    // per instantiation: the limit is raised once (one device per process)
     if (smem > 48 * 1024 && !raised) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -470,6 +547,18 @@ int launch(const MmaParams& p, dim3 grid, cudaStream_t s) {
 template <int HD>
 int launch_mode(const MmaParams& p, dim3 grid, bool key_split, cudaStream_t s) {
     return key_split ? launch<HD, true>(p, grid, s) : launch<HD, false>(p, grid, s);
+}
+
+template <int HD>
+int launch_mode_ext(const MmaParams& p, dim3 grid, bool key_split, cudaStream_t s) {
+    return key_split ? launch<HD, true, true>(p, grid, s) : launch<HD, false, true>(p, grid, s);
+}
+
+// the instantiated size that holds keys of hd and values of dv elements (0: none does)
+int ext_size(int hd, int dv) {
+    const int widest = hd > dv ? hd : dv;
+    if (hd <= 0 || dv <= 0 || hd % 8 != 0 || dv % 8 != 0 || widest > 128) return 0;
+    return widest <= 16 ? 16 : widest <= 32 ? 32 : widest <= 64 ? 64 : 128;
 }
 
 bool supported_head_dim(int hd) { return hd == 16 || hd == 32 || hd == 64 || hd == 128; }
@@ -517,6 +606,8 @@ extern "C" int tl_paged_attention_mma(const void* q, const void* k_pages, const 
     p.scale_log2 = scale * LOG2E;
     p.part_o = workspace;
     p.part_ml = workspace ? workspace + (size_t)n_tokens * n_heads * pl.n_splits * head_dim : nullptr;
+    p.hd = p.dv = head_dim; p.shared_kv = 0; p.keep_first = 0; p.rel = nullptr; p.bucket = nullptr; p.n_bucket = 0;
+    p.gate = nullptr; p.gate_mode = 0;
 
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid(pl.n_q_tiles * pl.n_splits, n_kv_heads * pl.n_gchunks, n_seqs);
@@ -531,6 +622,92 @@ extern "C" int tl_paged_attention_mma(const void* q, const void* k_pages, const 
     if (pl.n_splits > 1) {
         merge_partials_kernel<<<dim3((unsigned)n_tokens * (unsigned)n_heads), dim3(head_dim >= 128 ? 128u : 64u), 0, s>>>(
             p.part_o, p.part_ml, p.out, pl.n_splits, head_dim);
+        TL_LAUNCH_CHECK();
+    }
+    return TL_OK;
+}
+
+// ---- the extended form (see the top of this file).  Options as for the general kernel's
+// tl_paged_attention_ex; the struct is the same.
+struct TlAttentionOptions {
+    int v_head_dim;
+    int keep_first;
+    const float* rel;       // [rows, n_heads]
+    const int* bucket;      // [n_bucket]
+    int n_bucket;
+    const void* gate;       // bfloat16
+    int gate_mode;          // 0: none, 1: [tokens, n_heads], 2: [tokens, n_heads * v_head_dim]
+};
+
+// 1 if the extended form takes keys of head_dim and values of v_head_dim elements, else 0.
+extern "C" int tl_attention_mma_ex_supports(int head_dim, int v_head_dim) { return ext_size(head_dim, v_head_dim) ? 1 : 0; }
+
+extern "C" int tl_attention_mma_plan_ex(int n_tokens, int n_seqs, int n_heads, int n_kv_heads, int head_dim, int v_head_dim,
+                                        int max_q_len, int max_kv_len, int window, int keep_first, int allow_split,
+                                        int* n_splits, long long* workspace_floats) {
+    if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads != 0 || !ext_size(head_dim, v_head_dim)) return TL_BAD_SIZE;
+    const Plan pl = make_plan(n_seqs, n_heads, n_kv_heads, max_q_len, max_kv_len, allow_split, window, keep_first);
+    *n_splits = pl.n_splits;
+    *workspace_floats = pl.n_splits > 1 ? (long long)n_tokens * n_heads * pl.n_splits * (v_head_dim + 2) : 0;
+    return TL_OK;
+}
+
+// q: [n_tokens, n_heads, head_dim]; out: [n_tokens, n_heads, v_head_dim]; v_pages may be k_pages itself
+// (then v_head_dim must equal head_dim).  bfloat16 only.
+extern "C" int tl_paged_attention_mma_ex(const void* q, const void* k_pages, const void* v_pages, void* out,
+                                         const int* block_table, int table_stride, const int* q_start,
+                                         const int* kv_len, float* workspace, int n_tokens, int n_seqs,
+                                         int n_heads, int n_kv_heads, int head_dim, int page_size, int max_q_len,
+                                         int max_kv_len, int window, float scale, int allow_split,
+                                         const TlAttentionOptions* opt, void* stream) {
+    if (n_tokens <= 0 || n_seqs <= 0) return TL_OK;
+    if (opt == nullptr) return TL_BAD_SIZE;
+    if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads != 0 || page_size <= 0) return TL_BAD_SIZE;
+    const TlAttentionOptions o = *opt;
+    const int dv = o.v_head_dim > 0 ? o.v_head_dim : head_dim;
+    const int size = ext_size(head_dim, dv);
+    if (!size || max_q_len <= 0 || max_kv_len <= 0) return TL_BAD_SIZE;
+    if (window <= 0) window = 0;
+    if (o.keep_first < 0 || (o.keep_first > 0 && window == 0)) return TL_BAD_SIZE;
+    if (o.rel != nullptr && (o.bucket == nullptr || o.n_bucket <= 0)) return TL_BAD_SIZE;
+    if (o.gate_mode < 0 || o.gate_mode > 2 || (o.gate_mode != 0 && o.gate == nullptr)) return TL_BAD_SIZE;
+    if (v_pages == k_pages && dv != head_dim) return TL_BAD_SIZE;
+    if (!aligned16(q) || !aligned16(k_pages) || !aligned16(v_pages) || !aligned16(out)) return TL_BAD_ALIGN;
+    const Plan pl = make_plan(n_seqs, n_heads, n_kv_heads, max_q_len, max_kv_len, allow_split, window, o.keep_first);
+    if (pl.n_splits > 1 && workspace == nullptr) return TL_BAD_SIZE;
+    if (n_seqs > 65535 || (long long)n_kv_heads * pl.n_gchunks > 65535) return TL_BAD_SIZE;
+
+    MmaParams p;
+    p.q = (const __nv_bfloat16*)q; p.k_pages = (const __nv_bfloat16*)k_pages; p.v_pages = (const __nv_bfloat16*)v_pages;
+    p.out = (__nv_bfloat16*)out;
+    p.block_table = block_table; p.q_start = q_start; p.kv_len = kv_len; p.table_stride = table_stride;
+    p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.page_size = page_size;
+    p.page_shift = -1;
+    for (int sh = 0; sh < 31; ++sh)
+        if ((1 << sh) == page_size) p.page_shift = sh;
+    p.group = n_heads / n_kv_heads; p.ng = pl.ng; p.n_gchunks = pl.n_gchunks; p.tpw = pl.tpw;
+    p.window = window;
+    p.n_splits = pl.n_splits;
+    p.scale_log2 = scale * LOG2E;
+    p.part_o = workspace;
+    p.part_ml = workspace ? workspace + (size_t)n_tokens * n_heads * pl.n_splits * dv : nullptr;
+    p.hd = head_dim; p.dv = dv; p.shared_kv = v_pages == k_pages ? 1 : 0;
+    p.keep_first = o.keep_first; p.rel = o.rel; p.bucket = o.bucket; p.n_bucket = o.n_bucket;
+    p.gate = (const __nv_bfloat16*)o.gate; p.gate_mode = o.gate_mode;
+
+    cudaStream_t s = (cudaStream_t)stream;
+    dim3 grid(pl.n_q_tiles * pl.n_splits, n_kv_heads * pl.n_gchunks, n_seqs);
+    int rc;
+    switch (size) {
+        case 16: rc = launch_mode_ext<16>(p, grid, pl.key_split, s); break;
+        case 32: rc = launch_mode_ext<32>(p, grid, pl.key_split, s); break;
+        case 64: rc = launch_mode_ext<64>(p, grid, pl.key_split, s); break;
+        default: rc = launch_mode_ext<128>(p, grid, pl.key_split, s); break;
+    }
+    if (rc != TL_OK) return rc;
+    if (pl.n_splits > 1) {
+        merge_partials_kernel<<<dim3((unsigned)n_tokens * (unsigned)n_heads), dim3(dv >= 128 ? 128u : 64u), 0, s>>>(
+            p.part_o, p.part_ml, p.out, pl.n_splits, dv, p.gate, p.gate_mode);
         TL_LAUNCH_CHECK();
     }
     return TL_OK;

@@ -196,6 +196,10 @@ struct GemmParams {
     const float* in_ssq;
     int in_parts;
     float in_inv_dim, in_eps;
+    // gated form: which gate.  0: silu(g) * u.  1: the clamped form, g = min(g, limit), u = clamp(u, -limit, limit),
+    // g * sigmoid(alpha * g) * (u + up_offset)
+    int act_kind;
+    float act_limit, act_alpha, act_up_offset;
     // residual form
     int splits;             // = CTAs of a cluster
     float* h;               // [M, N] residual stream, updated in place
@@ -431,10 +435,17 @@ __global__ void __launch_bounds__(NTHREADS) gemm_tcgen05_kernel(const __grid_con
                                 // (rounded to bfloat16 first, as they are when they pass through memory:
                                 // this form and the two-kernel form give the same numbers)
                                 const float sc = scales[j];
-                                const float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[j]))) * sc;
-                                const float u = __bfloat162float(__float2bfloat16_rn(n_kb > 0 ? xch[row * (BQ + 1) + tok] : 0.f)) * sc;
-                                reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)tok * p.hidden + f] =
-                                    __float2bfloat16_rn(__fdividef(g, 1.f + __expf(-g)) * u);
+                                float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[j]))) * sc;
+                                float u = __bfloat162float(__float2bfloat16_rn(n_kb > 0 ? xch[row * (BQ + 1) + tok] : 0.f)) * sc;
+                                float y;
+                                if (p.act_kind == 0) {
+                                    y = __fdividef(g, 1.f + __expf(-g)) * u;
+                                } else {
+                                    g = fminf(g, p.act_limit);
+                                    u = fminf(fmaxf(u, -p.act_limit), p.act_limit);
+                                    y = g / (1.f + expf(-p.act_alpha * g)) * (u + p.act_up_offset);
+                                }
+                                reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)tok * p.hidden + f] = __float2bfloat16_rn(y);
                             }
                         }
                     }
@@ -731,9 +742,9 @@ extern "C" int tl_gemm_tcgen05_gated_supports(int M, int hidden, int K) {
 // (rows that were weighted for an RMS norm but not normalised yet).
 // Any hidden that is a multiple of 64 is computed correctly; tl_gemm_tcgen05_gated_supports says when
 // it is also the faster way.
-extern "C" int tl_gemm_tcgen05_gated(const void* A, const void* W, void* out, int M, int hidden, int K,
-                                     const float* in_ssq, int in_parts, float in_inv_dim, float in_eps, int* status,
-                                     void* stream) {
+static int gemm_gated(const void* A, const void* W, void* out, int M, int hidden, int K,
+                      const float* in_ssq, int in_parts, float in_inv_dim, float in_eps, int act_kind, float act_limit,
+                      float act_alpha, float act_up_offset, int* status, void* stream) {
     if (M <= 0 || hidden <= 0) return TL_OK;
     if (hidden % (BP / 2) != 0 || !tl_gemm_tcgen05_supports(M, 2 * hidden, K)) return TL_BAD_SIZE;
     if (!aligned16(A) || !aligned16(W) || !aligned16(out) || status == nullptr) return TL_BAD_ALIGN;
@@ -752,8 +763,23 @@ extern "C" int tl_gemm_tcgen05_gated(const void* A, const void* W, void* out, in
     p.hidden = hidden;
     p.splits = 1;
     p.in_ssq = in_ssq; p.in_parts = in_parts; p.in_inv_dim = in_inv_dim; p.in_eps = in_eps;
+    p.act_kind = act_kind; p.act_limit = act_limit; p.act_alpha = act_alpha; p.act_up_offset = act_up_offset;
     cudaStream_t s = (cudaStream_t)stream;
     if (bq == 16) return launch<16, 6, MODE_GATED>(mw, ma, p, slabs, 1, s);
     if (bq == 32) return launch<32, 5, MODE_GATED>(mw, ma, p, slabs, 1, s);
     return launch<64, 4, MODE_GATED>(mw, ma, p, slabs, 1, s);
+}
+
+extern "C" int tl_gemm_tcgen05_gated(const void* A, const void* W, void* out, int M, int hidden, int K,
+                                     const float* in_ssq, int in_parts, float in_inv_dim, float in_eps, int* status,
+                                     void* stream) {
+    return gemm_gated(A, W, out, M, hidden, K, in_ssq, in_parts, in_inv_dim, in_eps, 0, 0.f, 0.f, 0.f, status, stream);
+}
+
+// The same product with the clamped gate in its epilogue:
+// g = min(gate, limit), u = clamp(up, -limit, limit), out = g * sigmoid(alpha * g) * (u + up_offset).
+extern "C" int tl_gemm_tcgen05_gated_clamped(const void* A, const void* W, void* out, int M, int hidden, int K,
+                                             float limit, float alpha, float up_offset, int* status, void* stream) {
+    if (!(limit > 0.f)) return TL_BAD_SIZE;
+    return gemm_gated(A, W, out, M, hidden, K, nullptr, 0, 0.f, 0.f, 1, limit, alpha, up_offset, status, stream);
 }

@@ -134,6 +134,9 @@ class NativeOps:
         # bfloat16 value + bfloat16 remainder (2: a third slower, half the rounding error)
         self.prefill_probability_parts = int(os.environ.get("TORCHLLMS_B200_PREFILL_PARTS", "1"))
         self.use_fused_residual = os.environ.get("TORCHLLMS_B200_NO_FUSED_RESIDUAL", "") not in ("1", "true")
+        # attention with options (kept first keys, distance bias, gate, values of their own size) in bfloat16 on the
+        # tensor cores; TORCHLLMS_B200_NO_MMA_OPTIONS=1 keeps such calls on the CUDA-core kernel, for comparisons
+        self.use_mma_options = os.environ.get("TORCHLLMS_B200_NO_MMA_OPTIONS", "") not in ("1", "true")
 
     def graph_capturable(self, dtype: torch.dtype) -> bool:
         """Whether this library's launches for ``dtype`` may be recorded into a CUDA graph (not in
@@ -320,9 +323,35 @@ class NativeOps:
         return out
 
     def linear_glu(self, x: torch.Tensor, w_gate_up: torch.Tensor, *, limit: float, alpha: float, up_offset: float) -> torch.Tensor:
-        """The gate/up product over the stacked weight ``[2 H, K]`` and the clamped gate, in ``x``'s dtype."""
+        """The gate/up product over the stacked weight ``[2 H, K]`` and the clamped gate, in ``x``'s dtype.
+        Decode-sized bfloat16 inputs whose product needs no K split run as one kernel (the gate in the
+        product's epilogue), everything else as product + gate kernel."""
+        _cuda_contig(x, "linear input")
+        _cuda_contig(w_gate_up, "linear weight")
+        _need(x.dim() == 2 and w_gate_up.dim() == 2 and x.shape[1] == w_gate_up.shape[1] and w_gate_up.shape[0] % 2 == 0,
+              "linear_glu: x [M, K] against w [2 H, K]")
+        M, K = x.shape
+        hidden = w_gate_up.shape[0] // 2
+        if (x.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16 and self.use_tcgen05 and self.use_gated
+                and M <= 64 and hidden % 64 == 0 and K % 8 == 0 and K >= 8 and x.data_ptr() % 16 == 0
+                and w_gate_up.data_ptr() % 16 == 0
+                and self._lib("gemm_tcgen05").tl_gemm_tcgen05_gated_supports(M, hidden, K) == 1):
+            return self.gemm_gated_clamped(x, w_gate_up, limit, alpha, up_offset)
         return self.glu(self.linear(x, w_gate_up, partials_ok=True), out_dtype=x.dtype, limit=limit, alpha=alpha,
                         up_offset=up_offset)
+
+    @_timed
+    def gemm_gated_clamped(self, x: torch.Tensor, w_gate_up: torch.Tensor, limit: float, alpha: float, up_offset: float) -> torch.Tensor:
+        """The one-kernel form of :meth:`linear_glu` (its caller has checked the sizes)."""
+        M, K = x.shape
+        hidden = w_gate_up.shape[0] // 2
+        out = torch.empty((M, hidden), dtype=torch.bfloat16, device=x.device)
+        rc = self._lib("gemm_tcgen05").tl_gemm_tcgen05_gated_clamped(
+            _ptr(x), _ptr(w_gate_up), _ptr(out), M, hidden, K, ctypes.c_float(limit), ctypes.c_float(alpha),
+            ctypes.c_float(up_offset), ctypes.c_void_p(self._status.data_ptr()), _stream())
+        _check(rc, "gemm_tcgen05_gated_clamped")
+        self.launches += 1
+        return out
 
     @_timed
     def project_and_store(self, proj: torch.Tensor, *, n_q: int, n_k: int, n_v: int, n_extra: int,
@@ -681,10 +710,10 @@ class NativeOps:
         ``[T, H * v_dim]``, in q's dtype), by which the result is multiplied."""
         if keep_first or distance_bias is not None or gate is not None or v_pages.shape[-1] != q.shape[-1] \
                 or q.shape[-1] % 16 != 0:
-            _need(impl in ("auto", "general"), "only the general attention kernel takes these options")
+            _need(impl in ("auto", "general", "mma"), "only the general and the mma.sync attention kernels take these options")
             return self._paged_attention_general(q, k_pages, v_pages, block_table, q_start, kv_len, n_seqs, max_q_len,
                                                  max_kv_len, scale, window, page_size, allow_split, n_tokens, out,
-                                                 keep_first, distance_bias, distance_buckets, gate)
+                                                 keep_first, distance_bias, distance_buckets, gate, impl)
         _cuda_contig(q, "q")
         _cuda_contig(k_pages, "k_pages", q.dtype)
         _cuda_contig(v_pages, "v_pages", q.dtype)
@@ -779,8 +808,10 @@ class NativeOps:
 
     def _paged_attention_general(self, q, k_pages, v_pages, block_table, q_start, kv_len, n_seqs, max_q_len, max_kv_len,
                                  scale, window, page_size, allow_split, n_tokens, out, keep_first, distance_bias,
-                                 distance_buckets, gate) -> torch.Tensor:
-        """The CUDA-core kernel with everything it can do (see :meth:`paged_attention`)."""
+                                 distance_buckets, gate, impl: str = "general") -> torch.Tensor:
+        """The CUDA-core kernel with everything it can do (see :meth:`paged_attention`), or, with
+        ``impl`` "auto" or "mma", in bfloat16 and for sizes it takes (keys and values multiples of 8
+        up to 128), the extended form of the mma.sync kernel, which does the same."""
         _cuda_contig(q, "q")
         _cuda_contig(k_pages, "k_pages", q.dtype)
         _cuda_contig(v_pages, "v_pages", q.dtype)
@@ -818,6 +849,26 @@ class NativeOps:
                   "gate must be [tokens, heads] or [tokens, heads * v_dim]")
             opt.gate, opt.gate_mode = gate.data_ptr(), (1 if gate.shape[1] == n_heads and v_dim != 1 else 2)
         n_splits, floats = ctypes.c_int(0), ctypes.c_longlong(0)
+        mma_ok = (q.dtype == torch.bfloat16 and impl in ("auto", "mma") and self.use_mma_options
+                  and self._lib("attention_mma").tl_attention_mma_ex_supports(head_dim, v_dim) == 1
+                  and (v_pages.data_ptr() != k_pages.data_ptr() or v_dim == head_dim))
+        _need(impl != "mma" or mma_ok, "the mma.sync kernel takes bfloat16 and keys and values that are multiples of 8 up to 128")
+        if mma_ok:
+            lib = self._lib("attention_mma")
+            rc = lib.tl_attention_mma_plan_ex(T, n_seqs, n_heads, n_kv_heads, head_dim, v_dim, max_q_len, max_kv_len,
+                                              int(window or 0), int(keep_first), 1 if allow_split else 0,
+                                              ctypes.byref(n_splits), ctypes.byref(floats))
+            _check(rc, "attention_mma_plan")
+            ws = self._scratch(q.device, floats.value)
+            self._debug_limit("attention_mma", 0, k_pages.shape[0])
+            rc = lib.tl_paged_attention_mma_ex(
+                _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(block_table), block_table.stride(0),
+                _ptr(q_start), _ptr(kv_len), _ptr(ws), T, n_seqs, n_heads, n_kv_heads, head_dim,
+                page_size, max_q_len, max_kv_len, int(window or 0), ctypes.c_float(scale),
+                1 if allow_split else 0, ctypes.byref(opt), _stream())
+            _check(rc, "paged_attention_mma")
+            self.launches += 2 if n_splits.value > 1 else 1
+            return out
         lib = self._lib("attention")
         rc = lib.tl_attention_plan_ex(T, n_seqs, n_heads, n_kv_heads, head_dim, v_dim, max_q_len, max_kv_len,
                                       int(window or 0), int(keep_first), 1 if allow_split else 0,

@@ -216,5 +216,5 @@ class GatedBiasedAttention(Mixer):
             q.view(-1, self.n_heads, self.head_dim), cache.k_pages, cache.v_pages, cache.block_table, ctx.q_start,
             ctx.kv_len, n_seqs=ctx.n_seqs, max_q_len=ctx.max_q_len, max_kv_len=ctx.max_kv_len, scale=self.scale,
             window=self.window, page_size=cache.page_size, keep_first=self.keep_first,
-            distance_bias=self.distance_bias, distance_buckets=self.buckets, gate=gate, impl="general")
+            distance_bias=self.distance_bias, distance_buckets=self.buckets, gate=gate, impl="auto")
         return PendingProduct(o.view(o.shape[0], self.n_heads * self.v_head_dim), self.wo)

@@ -95,6 +95,6 @@ class LatentAttention(Mixer):
         o_lat = ops.paged_attention(
             q_lat, cache.k_pages, cache.k_pages, cache.block_table, ctx.q_start, ctx.kv_len,
             n_seqs=ctx.n_seqs, max_q_len=ctx.max_q_len, max_kv_len=ctx.max_kv_len, scale=self.scale,
-            window=self.window, page_size=cache.page_size, gate=gate, impl="general")
+            window=self.window, page_size=cache.page_size, gate=gate, impl="auto")
         o = ops.head_linear(o_lat, self.w_uv)                                                    # [T, H, v_head_dim]
         return PendingProduct(o.view(o.shape[0], self.n_heads * self.v_head_dim), self.wo)
