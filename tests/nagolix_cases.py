@@ -55,13 +55,13 @@ CASES = {
         latent_layer(heads=3, dim=8, vdim=16, kv_rank=24, size=17, kv_from=0, ff=None),
         attention_layer(heads=2, kv_heads=1, dim=32, vdim=16, size=7, keep_first=1, bias_max=30.0, ff=80, limit=0.7),
     ], width=64, vocab=97), 8, 12),
-    # awkward sizes: a width that is no multiple of 8, heads of 24 and 40, windows across page borders,
+    # awkward sizes: a width that is no multiple of 4, heads of 24 and 40, windows across page borders,
     # a borrowed latent behind a narrower window, one kv head per head, a tall bias table
     "awkward": (config([
         attention_layer(heads=3, kv_heads=3, dim=24, vdim=40, size=9, keep_first=5, bias_max=100.0, ff=50),
         latent_layer(heads=5, dim=12, vdim=20, kv_rank=36, size=13, ff=30),
         latent_layer(heads=1, dim=20, vdim=12, kv_rank=36, size=6, kv_from=1),
-    ], width=44, vocab=61, eps=1e-4, scale=3.0), 4, 20),
+    ], width=42, vocab=61, eps=1e-4, scale=3.0), 4, 20),
     # heads the tensor-core kernels like, a window longer than most prompts, nothing kept
     "wide": (config([
         attention_layer(heads=4, kv_heads=1, dim=64, vdim=64, size=300, keep_first=0, bias_max=200.0, ff=256),
@@ -136,12 +136,12 @@ def tokens_for(cfg: dict, n: int, seed: int = 0) -> List[int]:
 
 
 class Expected:
-    """The plain logits of a sequence and how far an engine may be from them.  In float32: 2e-4 on
-    every logit (they are of order one).  In bfloat16 the yardstick is what rounding itself does to
+    """The plain logits of a sequence and how far an engine may be from them.  In float32: 5e-5 of the
+    largest logit on every logit (2e-4 at least; the logits are of order one to ten).  In bfloat16 the yardstick is what rounding itself does to
     this model: the plain implementation is run a second time with bfloat16 rounding of every
     projection and activation, and a row of the engine's logits may differ from the exact ones
     (root mean square over the vocabulary) by three times what that emulation differs, the typical
-    row's figure standing in where a row's own is smaller."""
+    row's figure standing in where a row's own is smaller; one row in twenty may pass that, by half at most."""
 
     def __init__(self, cfg, tensors, tokens, dtype: str):
         self.dtype = dtype
@@ -158,12 +158,16 @@ class Expected:
         assert got.shape == self.logits.shape, f"{what}: {got.shape} logits for {self.logits.shape}"
         if self.dtype == "float32":
             err = np.abs(got - self.logits).max()
-            assert err <= 2e-4, f"{what}: logits differ by {err}"
+            limit = 5e-5 * max(4.0, float(np.abs(self.logits).max()))
+            assert err <= limit, f"{what}: logits differ by {err} (allowed {limit})"
         else:
             err = np.sqrt(((got - self.logits) ** 2).mean(-1))
             worst = int(np.argmax(err / self.allowed))
-            assert err[worst] <= self.allowed[worst], \
+            # (the emulation is one draw of the rounding noise and the engine's another: a row may pass its
+            # allowance by half, and one row in twenty may pass it at all)
+            assert err[worst] <= 1.5 * self.allowed[worst], \
                 f"{what}: row {worst} differs by {err[worst]} (rms), rounding alone allows {self.allowed[worst]}"
+            assert (err > self.allowed).mean() <= 0.05, f"{what}: {(err > self.allowed).sum()} of {len(err)} rows over their allowance"
 
 
 def plain_logits(cfg, tensors, tokens, dtype: str) -> Expected:

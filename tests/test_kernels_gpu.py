@@ -566,11 +566,11 @@ def test_prefill_attention_on_random_shapes(ops, seed):
 def test_attention_refuses_sizes_it_cannot_do(ops):
     from torchllms_b200.kernels.native import KernelError
     with pytest.raises(KernelError):
-        ops.check_attention_sizes(4, 2, 24, torch.float32, v_head_dim=264)     # values too wide
+        ops.check_attention_sizes(4, 2, 24, torch.float32, v_head_dim=520)     # values too wide
     with pytest.raises(KernelError):
         ops.check_attention_sizes(4, 3, 32, torch.float32)     # heads no multiple of kv heads
     with pytest.raises(KernelError):
-        ops.check_attention_sizes(4, 2, 512, torch.bfloat16)   # too wide
+        ops.check_attention_sizes(4, 2, 1024, torch.bfloat16)   # too wide
     with pytest.raises(KernelError):
         ops.embed(torch.zeros(3, dtype=torch.int32), torch.zeros(4, 4))  # CPU tensors
 

@@ -1,5 +1,5 @@
 // Causal grouped-query attention over paged keys and values, for any mix of prompt portions
-// and single decoded tokens (the general kernel: float32 and bfloat16, any head size up to 256
+// and single decoded tokens (the general kernel: float32 and bfloat16, any head size up to 512
 // for keys and, separately, for values, any number of heads and groups, optional sliding window).
 //
 // Options that a design may switch on, all off by default:
@@ -319,7 +319,8 @@ int launch_hd(const AttnParams& p, dim3 grid, cudaStream_t s) {
     const int widest = p.head_dim > p.v_head_dim ? p.head_dim : p.v_head_dim;
     if (widest <= 64) return launch<T, 64>(p, grid, s);
     if (widest <= 128) return launch<T, 128>(p, grid, s);
-    return launch<T, 256>(p, grid, s);
+    if (widest <= 256) return launch<T, 256>(p, grid, s);
+    return launch<T, 512>(p, grid, s);
 }
 
 }  // namespace
@@ -343,7 +344,7 @@ extern "C" int tl_attention_plan_ex(int n_tokens, int n_seqs, int n_heads, int n
                                     int allow_split, int* n_splits, long long* workspace_floats) {
     if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads != 0) return TL_BAD_SIZE;
     if (v_head_dim <= 0) v_head_dim = head_dim;
-    if (head_dim <= 0 || head_dim > 256 || v_head_dim > 256) return TL_BAD_SIZE;
+    if (head_dim <= 0 || head_dim > 512 || v_head_dim > 512) return TL_BAD_SIZE;
     const Plan pl = make_plan(n_seqs, n_heads, n_kv_heads, max_q_len, max_kv_len, allow_split, window, keep_first);
     *n_splits = pl.n_splits;
     *workspace_floats = pl.n_splits > 1 ? (long long)n_tokens * n_heads * pl.n_splits * (v_head_dim + 2) : 0;
@@ -374,7 +375,7 @@ extern "C" int tl_paged_attention_ex(const void* q, const void* k_pages, const v
     if (opt != nullptr) o = *opt;
     if (o.v_head_dim <= 0) o.v_head_dim = head_dim;
     if (window <= 0) window = 0;
-    if (head_dim <= 0 || head_dim > 256 || o.v_head_dim > 256) return TL_BAD_SIZE;
+    if (head_dim <= 0 || head_dim > 512 || o.v_head_dim > 512) return TL_BAD_SIZE;
     if (max_q_len <= 0 || max_kv_len <= 0) return TL_BAD_SIZE;
     if (o.keep_first < 0 || (o.keep_first > 0 && window == 0)) return TL_BAD_SIZE;
     if (o.rel != nullptr && (o.bucket == nullptr || o.n_bucket <= 0)) return TL_BAD_SIZE;

@@ -63,6 +63,7 @@ struct MmaParams {
     int n_bucket;
     const __nv_bfloat16* gate;
     int gate_mode;              // 0: none, 1: [T, n_heads], 2: [T, n_heads * dv]
+    int bias_cols;              // row split: the bias of so many distances (from 0) is tabulated in shared memory per head of the tile
 };
 
 __device__ __forceinline__ unsigned smem_addr(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -108,6 +109,7 @@ __global__ void __launch_bounds__(NT, KEY_SPLIT ? 4 : 2) attention_mma_kernel(co
     __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);    // [QROWS][PITCH]
     __nv_bfloat16* Ks = Qs + QROWS * PITCH;                            // [2][BN][PITCH]
     __nv_bfloat16* Vs = Ks + 2 * BN * PITCH;                           // [2][BN][PITCH]
+    float* Bs = reinterpret_cast<float*>(Vs + 2 * BN * PITCH);         // [ng][bias_cols] (EXT, row split, with a bias)
 
     const int b = blockIdx.z;
     const int qs = p.q_start[b];
@@ -137,6 +139,14 @@ __global__ void __launch_bounds__(NT, KEY_SPLIT ? 4 : 2) attention_mma_kernel(co
             v = *reinterpret_cast<const uint4*>(p.q + ((size_t)(qs + tok) * p.n_heads + head) * hd + part * 8);
         }
         *reinterpret_cast<uint4*>(Qs + r * PITCH + part * 8) = v;
+    }
+
+    // ---- the bias by distance of the tile's heads, on the base-2 scale (a prompt's CTA asks for the same few
+    // hundred distances tens of thousands of times)
+    const int bias_cols = (EXT && !KEY_SPLIT && p.rel != nullptr) ? p.bias_cols : 0;
+    for (int c = tid; c < ng * bias_cols; c += NT) {
+        const int hl = c / bias_cols, d = c - hl * bias_cols;
+        Bs[c] = __ldg(p.rel + (size_t)__ldg(p.bucket + min(d, p.n_bucket - 1)) * p.n_heads + kvh * p.group + g0 + hl) * LOG2E;
     }
 
     // ---- which keys this CTA walks
@@ -266,7 +276,19 @@ __global__ void __launch_bounds__(NT, KEY_SPLIT ? 4 : 2) attention_mma_kernel(co
             const float sl = biased ? 1.f : p.scale_log2;       // biased scores are put on the base-2 scale below
             const bool all_visible = share_hi <= k_hi && share_hi - 1 <= warp_qmin &&
                                      (p.window <= 0 || share_lo > warp_qmax - p.window);
-            if (biased) {
+            if (biased && all_visible && warp_qmax - share_lo < bias_cols) {
+                // every key of the share counts for every row and every distance is in the table
+                const float* brow[2] = {Bs + (g % ng) * bias_cols + (qpos[0] - share_lo - 2 * t),
+                                        Bs + ((g + 8) % ng) * bias_cols + (qpos[1] - share_lo - 2 * t)};
+                if (qpos[0] < 0) brow[0] = brow[1];          // a row without a query: any valid address (it is never stored)
+                if (qpos[1] < 0) brow[1] = brow[0];
+#pragma unroll
+                for (int nt = 0; nt < 2 * KG; ++nt) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e)
+                        s[nt][e] = fmaf(s[nt][e], p.scale_log2, brow[e >> 1][-(nt * 8 + (e & 1))]);
+                }
+            } else if (biased) {
                 // score * scale + rel[bucket[distance], head], on the base-2 scale; hidden keys get -inf
                 int head[2];
 #pragma unroll
@@ -281,8 +303,15 @@ __global__ void __launch_bounds__(NT, KEY_SPLIT ? 4 : 2) attention_mma_kernel(co
                                         (p.window <= 0 || kpos > qpos[i] - p.window || kpos < p.keep_first);
                         float v = -INFINITY;
                         if (ok) {
-                            const int row = __ldg(p.bucket + min(qpos[i] - kpos, p.n_bucket - 1));
-                            v = fmaf(s[nt][e], p.scale_log2, __ldg(p.rel + (size_t)row * p.n_heads + head[i]) * LOG2E);
+                            const int dist = qpos[i] - kpos;
+                            float bias;
+                            if (dist < bias_cols) {
+                                bias = Bs[((g + 8 * i) % ng) * bias_cols + dist];
+                            } else {
+                                const int row = __ldg(p.bucket + min(dist, p.n_bucket - 1));
+                                bias = __ldg(p.rel + (size_t)row * p.n_heads + head[i]) * LOG2E;
+                            }
+                            v = fmaf(s[nt][e], p.scale_log2, bias);
                         }
                         s[nt][e] = v;
                     }
@@ -530,14 +559,15 @@ int launch(const MmaParams& p, dim3 grid, cudaStream_t s) {
     constexpr int PITCH = HD + 8;
     constexpr int QROWS = KEY_SPLIT ? 16 : 16 * NW;
     size_t smem = (size_t)(QROWS + 4 * BN) * PITCH * sizeof(__nv_bfloat16);
+    if (EXT && !KEY_SPLIT && p.rel != nullptr) smem += (size_t)p.ng * p.bias_cols * sizeof(float);
     const size_t merge = KEY_SPLIT ? (size_t)(NW * 16 * (HD + 2)) * sizeof(float) : 0;
     if (merge > smem) smem = merge;
     auto kern = attention_mma_kernel<HD, KEY_SPLIT, EXT>;
-    static bool raised = false;    // per instantiation: the limit is raised once (one device per process)
-    if (smem > 48 * 1024 && !raised) {
+    static size_t raised = 48 * 1024;    // per instantiation: the largest limit set so far (one device per process)
+    if (smem > raised) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
-        raised = true;
+        raised = smem;
     }
     kern<<<grid, NT, smem, s>>>(p);
     TL_LAUNCH_CHECK();
@@ -607,7 +637,7 @@ extern "C" int tl_paged_attention_mma(const void* q, const void* k_pages, const 
     p.part_o = workspace;
     p.part_ml = workspace ? workspace + (size_t)n_tokens * n_heads * pl.n_splits * head_dim : nullptr;
     p.hd = p.dv = head_dim; p.shared_kv = 0; p.keep_first = 0; p.rel = nullptr; p.bucket = nullptr; p.n_bucket = 0;
-    p.gate = nullptr; p.gate_mode = 0;
+    p.gate = nullptr; p.gate_mode = 0; p.bias_cols = 0;
 
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid(pl.n_q_tiles * pl.n_splits, n_kv_heads * pl.n_gchunks, n_seqs);
@@ -694,6 +724,15 @@ extern "C" int tl_paged_attention_mma_ex(const void* q, const void* k_pages, con
     p.hd = head_dim; p.dv = dv; p.shared_kv = v_pages == k_pages ? 1 : 0;
     p.keep_first = o.keep_first; p.rel = o.rel; p.bucket = o.bucket; p.n_bucket = o.n_bucket;
     p.gate = (const __nv_bfloat16*)o.gate; p.gate_mode = o.gate_mode;
+    // distances a row-split CTA meets inside its window (all of them when there is no window), as far as
+    // 20 KB of shared memory hold them for the heads of a tile
+    p.bias_cols = 0;
+    if (o.rel != nullptr && !pl.key_split) {
+        long long cols = window > 0 ? (long long)window + pl.tpw * NW : max_kv_len;
+        if (cols > o.n_bucket) cols = o.n_bucket;
+        if (cols > 5120 / pl.ng) cols = 5120 / pl.ng;
+        p.bias_cols = (int)cols;
+    }
 
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid(pl.n_q_tiles * pl.n_splits, n_kv_heads * pl.n_gchunks, n_seqs);

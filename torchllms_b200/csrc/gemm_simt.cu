@@ -97,6 +97,39 @@ extern "C" int tl_gemm_simt(const void* A, const void* W, void* C, int in_dtype,
     return TL_BAD_DTYPE;
 }
 
+namespace {
+
+// Few rows (decode steps): a CTA per (head, token); the token's K inputs in shared memory as float32,
+// a thread per output column walking that column's K weights 16 bytes at a time where K allows.
+template <typename T>
+__global__ void __launch_bounds__(128) head_linear_rows_kernel(const T* __restrict__ x, const T* __restrict__ w,
+                                                               T* __restrict__ out, int n_heads, int N, int K) {
+    extern __shared__ __align__(16) float xs[];
+    const int h = blockIdx.x, t = blockIdx.y;
+    const T* xr = x + ((size_t)t * n_heads + h) * K;
+    for (int k = threadIdx.x; k < K; k += blockDim.x) xs[k] = to_float(xr[k]);
+    __syncthreads();
+    constexpr int VEC = Vec16<T>::N;
+    const bool vec = K % VEC == 0 && ((size_t)w & 15u) == 0;
+    for (int n = threadIdx.x; n < N; n += blockDim.x) {
+        const T* wr = w + ((size_t)h * N + n) * K;
+        float acc = 0.f;
+        if (vec) {
+            for (int k = 0; k < K; k += VEC) {
+                Vec16<T> v;
+                v.load(wr + k);
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) acc = fmaf(v.get(e), xs[k + e], acc);
+            }
+        } else {
+            for (int k = 0; k < K; ++k) acc = fmaf(to_float(wr[k]), xs[k], acc);
+        }
+        out[((size_t)t * n_heads + h) * N + n] = from_float<T>(acc);
+    }
+}
+
+}  // namespace
+
 // One product per head: x [tokens, heads, K] against w [heads, N, K] gives out [tokens, heads, N],
 // out[t, h, :] = w[h] x[t, h, :]; x, w and out have one dtype.
 extern "C" int tl_head_linear(const void* x, const void* w, void* out, int dtype, int n_tokens, int n_heads,
@@ -104,6 +137,19 @@ extern "C" int tl_head_linear(const void* x, const void* w, void* out, int dtype
     if (n_tokens <= 0 || n_heads <= 0 || N <= 0) return TL_OK;
     if (K <= 0) return TL_BAD_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
+    if (n_tokens <= 16 && n_heads <= 65535 && (size_t)K * sizeof(float) <= 48 * 1024) {
+        const dim3 grid(n_heads, n_tokens);
+        if (dtype == TL_F32)
+            head_linear_rows_kernel<float><<<grid, 128, (size_t)K * sizeof(float), s>>>((const float*)x, (const float*)w, (float*)out,
+                                                                                         n_heads, N, K);
+        else if (dtype == TL_BF16)
+            head_linear_rows_kernel<__nv_bfloat16><<<grid, 128, (size_t)K * sizeof(float), s>>>(
+                (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, n_heads, N, K);
+        else
+            return TL_BAD_DTYPE;
+        TL_LAUNCH_CHECK();
+        return TL_OK;
+    }
     const long long lda = (long long)n_heads * K, ldc = (long long)n_heads * N;
     if (dtype == TL_F32)
         return launch<float, float>(x, w, out, n_tokens, N, K, s, n_heads, lda, ldc, K, (long long)N * K, N);

@@ -186,6 +186,165 @@ __global__ void project_store_kernel(const ProjectParams p) {
     }
 }
 
+
+// ---- four columns at a time (widths that are multiples of 4, rows that start on 16 bytes)
+__device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 ld4(const __nv_bfloat16* p) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void st4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void st4(__nv_bfloat16* p, float4 v) {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 raw;
+    raw.x = *reinterpret_cast<const unsigned*>(&a);
+    raw.y = *reinterpret_cast<const unsigned*>(&b);
+    *reinterpret_cast<uint2*>(p) = raw;
+}
+// the sum over the planes of a split-K product (or the one plane there is), four columns
+template <typename T>
+__device__ __forceinline__ float4 sum_planes4(const T* p, int splits, long long plane) {
+    float4 v = ld4(p);
+#pragma unroll 4
+    for (int s = 1; s < splits; ++s) {
+        const float4 w = ld4(p + (size_t)s * plane);
+        v.x += w.x; v.y += w.y; v.z += w.z; v.w += w.w;
+    }
+    return v;
+}
+
+template <typename TD>
+__global__ void norm_add_vec_kernel(float* __restrict__ h, const TD* __restrict__ delta, int splits, long long plane,
+                                    const float* __restrict__ weight, __nv_bfloat16* __restrict__ rows_out, int dim,
+                                    float eps) {
+    extern __shared__ __align__(16) float row_buf[];
+    __shared__ float part[33];
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const size_t base = (size_t)blockIdx.x * dim;
+    float ssq = 0.f;
+    for (int d = threadIdx.x * 4; d < dim; d += blockDim.x * 4) {
+        const float4 v = sum_planes4(delta + base + d, splits, plane);
+        st4(row_buf + d, v);
+        ssq += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+    const float r = rsqrtf(block_sum(ssq, part) / (float)dim + eps);
+    for (int d = threadIdx.x * 4; d < dim; d += blockDim.x * 4) {
+        const float4 x = ld4(row_buf + d), w = ld4(weight + d);
+        float4 v = ld4(h + base + d);
+        v.x += x.x * r * w.x; v.y += x.y * r * w.y; v.z += x.z * r * w.z; v.w += x.w * r * w.w;
+        st4(h + base + d, v);
+        if (rows_out != nullptr) st4(rows_out + base + d, v);
+    }
+}
+
+// bfloat16 in and out, one plane, hidden a multiple of 8: eight gates and eight ups per thread and turn
+__global__ void glu_clamped_bf16x8_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out,
+                                          long long n_chunks, int chunks_per_row, float limit, float alpha, float up_offset) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n_chunks; i += (long long)gridDim.x * blockDim.x) {
+        const long long t = i / chunks_per_row;
+        const int c = (int)(i - t * chunks_per_row);
+        const size_t hidden = (size_t)chunks_per_row * 8;
+        const __nv_bfloat16* g = in + (size_t)t * 2 * hidden + (size_t)c * 8;
+        Vec16<__nv_bfloat16> gv, uv, ov;
+        gv.load(g);
+        uv.load(g + hidden);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const float a = fminf(gv.get(e), limit);
+            const float u = fminf(fmaxf(uv.get(e), -limit), limit);
+            ov.set(e, __fdividef(a, 1.f + __expf(-alpha * a)) * (u + up_offset));
+        }
+        ov.store(out + (size_t)t * hidden + (size_t)c * 8);
+    }
+}
+
+// project_store, four columns at a time: every part of the row ([q | k | v | extra]) and every head's
+// share of it is a multiple of 4 wide
+template <typename TI, typename TO>
+__global__ void project_store_vec_kernel(const ProjectParams p) {
+    extern __shared__ __align__(16) float row[];
+    __shared__ float part[33];
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const int t = blockIdx.x;
+    const int width = p.n_q + p.n_k + p.n_v + p.n_extra;
+    const TI* in = reinterpret_cast<const TI*>(p.proj) + (size_t)t * width;
+    float ssq_q = 0.f, ssq_k = 0.f;
+    for (int c = threadIdx.x * 4; c < width; c += blockDim.x * 4) {
+        float4 v = sum_planes4(in + c, p.splits, p.plane);
+        if (p.bias != nullptr) {
+            const float4 b = ld4(p.bias + c);
+            v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+        }
+        st4(row + c, v);
+        const float sq = v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        if (c < p.n_q) ssq_q += sq;
+        else if (c < p.n_q + p.n_k) ssq_k += sq;
+    }
+    float rq = 1.f, rk = 1.f;
+    if (p.q_norm != nullptr) rq = rsqrtf(block_sum(ssq_q, part) / (float)p.n_q + p.eps);
+    if (p.k_norm != nullptr && p.n_k > 0) rk = rsqrtf(block_sum(ssq_k, part) / (float)p.n_k + p.eps);
+    __syncthreads();
+
+    TO* q_out = reinterpret_cast<TO*>(p.q_out) + (size_t)t * p.n_q;
+    for (int c = threadIdx.x * 4; c < p.n_q; c += blockDim.x * 4) {
+        float4 v = ld4(row + c);
+        if (p.q_norm != nullptr) {
+            const float4 w = ld4(p.q_norm + c);
+            v.x *= rq * w.x; v.y *= rq * w.y; v.z *= rq * w.z; v.w *= rq * w.w;
+        }
+        st4(q_out + c, v);
+    }
+    if (p.k_pages != nullptr && p.n_k > 0) {
+        const int slot = p.slot_mapping[t];
+        if (TL_CHECK(slot >= 0, TL_DBG_SLOT) && tl_check_page(slot / p.page_size)) {
+            const size_t page = slot / p.page_size, off = slot % p.page_size;
+            TO* kp = reinterpret_cast<TO*>(p.k_pages);
+            const float* k = row + p.n_q;
+            for (int c = threadIdx.x * 4; c < p.n_k; c += blockDim.x * 4) {
+                const int head = c / p.k_dim, d = c - head * p.k_dim;
+                float4 v = ld4(k + c);
+                if (p.k_norm != nullptr) {
+                    const float4 w = ld4(p.k_norm + c);
+                    v.x *= rk * w.x; v.y *= rk * w.y; v.z *= rk * w.z; v.w *= rk * w.w;
+                }
+                st4(kp + ((page * p.n_kv_heads + head) * p.page_size + off) * p.k_dim + d, v);
+            }
+            if (p.v_pages != nullptr && p.n_v > 0) {
+                TO* vp = reinterpret_cast<TO*>(p.v_pages);
+                const float* vv = row + p.n_q + p.n_k;
+                for (int c = threadIdx.x * 4; c < p.n_v; c += blockDim.x * 4) {
+                    const int head = c / p.v_dim, d = c - head * p.v_dim;
+                    st4(vp + ((page * p.n_kv_heads + head) * p.page_size + off) * p.v_dim + d, ld4(vv + c));
+                }
+            }
+        }
+    }
+    if (p.n_extra > 0) {
+        TO* e_out = reinterpret_cast<TO*>(p.extra_out) + (size_t)t * p.n_extra;
+        const float* e = row + p.n_q + p.n_k + p.n_v;
+        for (int c = threadIdx.x * 4; c < p.n_extra; c += blockDim.x * 4) {
+            const float4 v = ld4(e + c);
+            st4(e_out + c, make_float4(1.f / (1.f + expf(-v.x)), 1.f / (1.f + expf(-v.y)), 1.f / (1.f + expf(-v.z)),
+                                       1.f / (1.f + expf(-v.w))));
+        }
+    }
+}
+
+// A thread to four columns, in whole warps: at most 1,024 threads for the few rows of a decode step (a row is
+// a CTA: the row's latency is the kernel's), at most 256 where rows are many (several CTAs share an SM and the
+// block-wide sums cost less).
+inline int vec_threads(int cols, int n_rows) {
+    int t = ((cols / 4 + 31) / 32) * 32;
+    const int most = n_rows > 256 ? 256 : 1024;
+    return t < 64 ? 64 : (t > most ? most : t);
+}
+
 inline int row_threads(int dim) { return dim >= 2048 ? 512 : (dim >= 512 ? 256 : 128); }
 
 }  // namespace
@@ -229,6 +388,14 @@ extern "C" int tl_norm_add(float* h, const void* delta, int delta_dtype, int spl
     if (smem > 200 * 1024) return TL_TOO_LARGE;
     cudaStream_t s = (cudaStream_t)stream;
     cudaError_t e;
+    const bool vec = dim % 4 == 0 && plane % 4 == 0 && aligned16(h) && aligned16(delta) && aligned16(weight) &&
+                     (rows_out == nullptr || aligned16(rows_out)) && smem <= 48 * 1024;
+    if (vec && delta_dtype == TL_F32)
+        return (int)tl_launch(norm_add_vec_kernel<float>, dim3(n_rows), dim3(vec_threads(dim, n_rows)), smem, s, h, (const float*)delta,
+                              splits, plane, weight, (__nv_bfloat16*)rows_out, dim, eps);
+    if (vec && delta_dtype == TL_BF16)
+        return (int)tl_launch(norm_add_vec_kernel<__nv_bfloat16>, dim3(n_rows), dim3(vec_threads(dim, n_rows)), smem, s, h,
+                              (const __nv_bfloat16*)delta, splits, plane, weight, (__nv_bfloat16*)rows_out, dim, eps);
     if (delta_dtype == TL_F32) {
         static int raised = 0;
         if (smem > 48 * 1024 && (int)smem > raised) {
@@ -263,6 +430,13 @@ extern "C" int tl_glu_clamped(const void* in, int in_dtype, int splits, long lon
     if (blocks > 148 * 16) blocks = 148 * 16;
     const dim3 grid((unsigned)blocks), block(256);
     cudaError_t e;
+    if (in_dtype == TL_BF16 && out_dtype == TL_BF16 && splits == 1 && hidden % 8 == 0 && aligned16(in) && aligned16(out)) {
+        const long long n_chunks = (long long)n_tokens * (hidden / 8);
+        long long b8 = (n_chunks + 255) / 256;
+        if (b8 > 148 * 16) b8 = 148 * 16;
+        return (int)tl_launch(glu_clamped_bf16x8_kernel, dim3((unsigned)b8), block, 0, s, (const __nv_bfloat16*)in,
+                              (__nv_bfloat16*)out, n_chunks, hidden / 8, limit, alpha, up_offset);
+    }
     if (in_dtype == TL_F32 && out_dtype == TL_F32)
         e = tl_launch(glu_clamped_kernel<float, float>, grid, block, 0, s, (const float*)in, splits, plane, (float*)out,
                       (long long)n_tokens, hidden, limit, alpha, up_offset);
@@ -299,6 +473,18 @@ extern "C" int tl_project_store(const void* proj, int in_dtype, int splits, long
     p.n_kv_heads = n_kv_heads; p.k_dim = k_dim; p.v_dim = v_dim;
     cudaStream_t s = (cudaStream_t)stream;
     cudaError_t e;
+    const bool vec = n_q % 4 == 0 && n_k % 4 == 0 && n_v % 4 == 0 && n_extra % 4 == 0 && plane % 4 == 0 &&
+                     (k_pages == nullptr || n_k == 0 || (k_dim % 4 == 0 && aligned16(k_pages))) &&
+                     (v_pages == nullptr || n_v == 0 || (v_dim % 4 == 0 && aligned16(v_pages))) && aligned16(proj) &&
+                     aligned16(q_out) && (extra_out == nullptr || aligned16(extra_out)) && (bias == nullptr || aligned16(bias)) &&
+                     (q_norm == nullptr || aligned16(q_norm)) && (k_norm == nullptr || aligned16(k_norm)) && smem <= 48 * 1024;
+    if (vec) {
+        const dim3 grid(n_tokens), block(vec_threads(width, n_tokens));
+        if (in_dtype == TL_F32 && out_dtype == TL_F32) return (int)tl_launch(project_store_vec_kernel<float, float>, grid, block, smem, s, p);
+        if (in_dtype == TL_F32 && out_dtype == TL_BF16) return (int)tl_launch(project_store_vec_kernel<float, __nv_bfloat16>, grid, block, smem, s, p);
+        if (in_dtype == TL_BF16 && out_dtype == TL_BF16) return (int)tl_launch(project_store_vec_kernel<__nv_bfloat16, __nv_bfloat16>, grid, block, smem, s, p);
+        return TL_BAD_DTYPE;
+    }
 #define TL_PROJECT_LAUNCH(TI, TO)                                                                                      \
     do {                                                                                                               \
         static int raised = 0;                                                                                         \

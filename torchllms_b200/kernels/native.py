@@ -183,13 +183,13 @@ class NativeOps:
     # ------------------------------------------------------------- checks
     def check_attention_sizes(self, n_heads: int, n_kv_heads: int, head_dim: int, dtype: torch.dtype,
                               v_head_dim: Optional[int] = None) -> None:
-        """The general kernel takes any head size up to 256 (keys and values separately); the
+        """The general kernel takes any head size up to 512 (keys and values separately); the
         tensor-core kernels take their own few sizes and are chosen only where they apply."""
         _need(dtype in _DT, f"attention supports float32 and bfloat16, not {dtype}")
         _need(n_heads > 0 and n_kv_heads > 0 and n_heads % n_kv_heads == 0,
               f"n_heads ({n_heads}) must be a positive multiple of n_kv_heads ({n_kv_heads})")
-        _need(1 <= head_dim <= 256, f"head_dim must lie between 1 and 256, got {head_dim}")
-        _need(v_head_dim is None or 1 <= v_head_dim <= 256, f"v_head_dim must lie between 1 and 256, got {v_head_dim}")
+        _need(1 <= head_dim <= 512, f"head_dim must lie between 1 and 512, got {head_dim}")
+        _need(v_head_dim is None or 1 <= v_head_dim <= 512, f"v_head_dim must lie between 1 and 512, got {v_head_dim}")
 
     # ------------------------------------------------------------ elementwise
     @_timed
@@ -405,13 +405,18 @@ class NativeOps:
     @_timed
     def head_linear(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
         """One small product per head: ``x [T, H, K]`` against ``w [H, N, K]`` gives ``[T, H, N]``,
-        ``out[t, h] = w[h] @ x[t, h]`` (float32 multiply-adds on the CUDA cores in both dtypes)."""
+        ``out[t, h] = w[h] @ x[t, h]``: float32 multiply-adds on the CUDA cores (a kernel of its own for
+        the few rows of a decode step), except bfloat16 with more than 64 rows, which goes to the library's
+        batched product."""
         _cuda_contig(x, "head_linear input")
         _cuda_contig(w, "head_linear weight", x.dtype)
         _need(x.dim() == 3 and w.dim() == 3 and x.shape[1] == w.shape[0] and x.shape[2] == w.shape[2] and x.dtype in _DT,
               "head_linear: x [T, H, K] against w [H, N, K]")
         T, H, K = x.shape
         N = w.shape[1]
+        if x.dtype == torch.bfloat16 and T > 64:
+            # prompt portions: the library's batched product, as linear() does for so many rows
+            return torch.bmm(x.transpose(0, 1), w.transpose(1, 2)).transpose(0, 1).contiguous()
         out = torch.empty((T, H, N), dtype=x.dtype, device=x.device)
         _check(self._lib("gemm_simt").tl_head_linear(_ptr(x), _ptr(w), _ptr(out), _DT[x.dtype], T, H, N, K, _stream()), "head_linear")
         self.launches += 1

@@ -240,7 +240,10 @@ def adapt_tensors(cfg: NagolixConfig, found: Dict[str, LazyTensor]) -> Dict[str,
     """The checkpoint's names to the parts' names; anything unknown keeps its name, so that the
     strict check reports it."""
     out: Dict[str, LazyTensor] = {}
+    no_ffn = {f"l{i}.norm2" for i, layer in enumerate(cfg.layers) if layer.mlp is None}
     for name, t in found.items():
+        if name in no_ffn:
+            continue                 # a second norm stored for a layer that has no feed-forward: nothing reads it
         new = _TOP_NAMES.get(name, name)
         m = _LAYER_RE.match(name)
         if m and m.group(2) in _LAYER_NAMES:
