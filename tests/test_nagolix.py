@@ -332,3 +332,23 @@ def test_attention_kernels_with_options_on_random_shapes(dtype):
             torch.testing.assert_close(got, want, atol=tol, rtol=tol, msg=lambda m: (
                 f"{impl} case {case}: seq {seq_lens} q {q_lens} H{H} KV{KV} hd{hd} dv{dv} P{P} window {window} keep {keep} "
                 f"bias {'distance_bias' in kw} gate {mode} shared {shared}: {m}"))
+
+
+def test_random_weights_mode_writes_a_folder_that_loads(tmp_path):
+    """The framework's random-weights mode for this architecture: a folder under the checkpoint's
+    names that loads like any other, and the same model built without a file."""
+    from torchllms_b200.config.registry import load_config
+    from torchllms_b200.engine.loading import load_model, random_model
+    from torchllms_b200.weights.random_init import write_random_model
+    from torchllms_b200.weights.safetensors_io import TensorSource
+    from torch_ops import TorchOps
+    cfg, _tensors, folder, _page = nc.case_folder(tmp_path, "mixed")
+    _arch, parsed = load_config(folder)
+    out = write_random_model(tmp_path / "random", parsed, seed=3)
+    names = set(TensorSource(out).names())
+    assert {"embed", "pos", "final.norm", "l0.mix.dkv", "l1.mix.rel", "l2.mix.uk", "l3.mlp.down"} <= names
+    assert "l2.mix.dkv" not in names and "l2.norm2" not in names       # borrowed latents; no feed-forward
+    _, _, from_file = load_model(out, dtype="float32", device="cpu", ops=TorchOps())
+    _, _, direct = random_model(parsed, 3, dtype="float32", device="cpu", ops=TorchOps())
+    assert torch.equal(from_file.embedding, direct.embedding)
+    assert torch.equal(from_file.blocks[1].mixer.w_in, direct.blocks[1].mixer.w_in)

@@ -78,7 +78,11 @@ def random_model(config, seed: int, *, dtype="bfloat16", device="cuda", arch: Op
     arch = arch or get_architecture(config.architecture)
     model = Model(arch.build_spec(config), dtype=parse_dtype(dtype), device=device, ops=ops or get_ops(),
                   max_positions=max_positions)
+    # the architecture draws its tensors under the names a checkpoint of it uses; they take the same
+    # way to the parts' names as a checkpoint's do
     tensors: Dict[str, torch.Tensor] = dict(arch.random_tensors(config, seed, device=device, dtype=model.dtype))
-    check_tensors("random weights", model.expected_tensors(), {k: LazyTensor.of(v) for k, v in tensors.items()})
-    model.load(tensors)
+    found = arch.adapt_tensors(config, {k: LazyTensor.of(v) for k, v in tensors.items()})
+    expected = model.expected_tensors()
+    check_tensors("random weights", expected, found)
+    model.load(materialize(expected, found))
     return arch, config, model

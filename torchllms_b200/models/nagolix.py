@@ -291,11 +291,10 @@ def tensor_shapes(cfg: NagolixConfig, bias_rows: int = 16) -> Iterator[Tuple[str
 
 
 def random_tensors(cfg: NagolixConfig, seed: int, *, device="cpu", dtype: torch.dtype = torch.float32,
-                   bias_rows: int = 16, native_names: bool = True) -> Iterator[Tuple[str, torch.Tensor]]:
-    """Seeded random weights (one generator, one order, drawn in float32, then cast): matrices
-    ``N(0, 1/fan_in)``, the table's rows of unit size over the embedding's scale, norm weights
-    around zero, gains around one.  ``native_names``: the parts' names (for a model that is loaded
-    straight away) or the checkpoint's (for a folder)."""
+                   bias_rows: int = 16) -> Iterator[Tuple[str, torch.Tensor]]:
+    """Seeded random weights under the checkpoint's names (one generator, one order, drawn in
+    float32, then cast): matrices ``N(0, 1/fan_in)``, the table's rows of unit size over the
+    embedding's scale, norm weights around zero, gains around one."""
     gen = torch.Generator(device=device)
     gen.manual_seed(int(seed))
     for name, shape, init in tensor_shapes(cfg, bias_rows):
@@ -308,9 +307,6 @@ def random_tensors(cfg: NagolixConfig, seed: int, *, device="cpu", dtype: torch.
             t = t * 0.1
         elif init == "gain":
             t = 1.0 + t * 0.1
-        if native_names:
-            m = _LAYER_RE.match(name)
-            name = f"{m.group(1)}.{_LAYER_NAMES[m.group(2)]}" if m else _TOP_NAMES.get(name, name)
         yield name, t.to(dtype)
 
 
