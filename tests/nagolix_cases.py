@@ -24,14 +24,14 @@ import plain_nagolix as plain
 
 
 def attention_layer(heads=4, kv_heads=2, dim=16, vdim=16, size=12, keep_first=2, bias_max=40.0, scale=None, ff=48,
-                    limit=1.5):
+                    limit=2.0):
     return {"type": "attention",
             "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "bias_max": bias_max,
                       "mask": {"size": size, "keep_first": keep_first}, "scale": scale or dim ** -0.5},
             "mlp": None if ff is None else {"kind": "dense", "ff": ff, "limit": limit}}
 
 
-def latent_layer(heads=2, dim=16, vdim=16, kv_rank=24, size=20, kv_from=None, scale=None, ff=48, limit=1.5):
+def latent_layer(heads=2, dim=16, vdim=16, kv_rank=24, size=20, kv_from=None, scale=None, ff=48, limit=2.0):
     mixer = {"heads": heads, "dim": dim, "vdim": vdim, "kv_rank": kv_rank, "mask": {"size": size},
              "scale": scale or dim ** -0.5}
     if kv_from is not None:
@@ -65,7 +65,7 @@ CASES = {
     # heads the tensor-core kernels like, a window longer than most prompts, nothing kept
     "wide": (config([
         attention_layer(heads=4, kv_heads=1, dim=64, vdim=64, size=300, keep_first=0, bias_max=200.0, ff=256),
-        latent_layer(heads=4, dim=32, vdim=32, kv_rank=64, size=300, ff=256),
+        latent_layer(heads=4, dim=64, vdim=32, kv_rank=128, size=300, ff=320),
     ], width=128, vocab=211, max_positions=512), 16, 6),
 }
 

@@ -352,3 +352,93 @@ def test_random_weights_mode_writes_a_folder_that_loads(tmp_path):
     _, _, direct = random_model(parsed, 3, dtype="float32", device="cpu", ops=TorchOps())
     assert torch.equal(from_file.embedding, direct.embedding)
     assert torch.equal(from_file.blocks[1].mixer.w_in, direct.blocks[1].mixer.w_in)
+
+
+# ---------------------------------------------------------------- the small kernels against the plain functions
+
+def _ops_for(backend):
+    if backend[0] == "cpu":
+        from torch_ops import TorchOps
+        return TorchOps(), "cpu", torch.float32
+    from torchllms_b200.kernels import get_ops
+    return get_ops(), "cuda", (torch.float32 if backend[1] == "float32" else torch.bfloat16)
+
+
+@pytest.mark.parametrize("backend", BACKENDS)
+def test_small_kernels_against_the_plain_functions(backend):
+    """Embedding with scale and positions, the norm of a sublayer's output with the residual sum
+    (also from split-K partial sums), the clamped gate (both forms on the GPU), the stacked
+    projection's kernel and the per-head products, each against the plain implementation's function,
+    at widths that are and are not multiples of four, for one row and for many."""
+    ops, dev, dtype = _ops_for(backend)
+    g = torch.Generator().manual_seed(3)
+    tol = dict(atol=2e-5, rtol=2e-5) if dtype == torch.float32 else dict(atol=3e-2, rtol=3e-2)
+    rnd = lambda *shape: torch.randn(*shape, generator=g)
+    for T, dim in ((1, 64), (7, 42), (130, 256), (9, 1032)):
+        # embedding
+        table, pos = rnd(50, dim).to(dtype), rnd(40, dim).to(dtype)
+        ids, at = torch.randint(0, 50, (T,), generator=g), torch.randint(0, 40, (T,), generator=g)
+        got = ops.embed(ids.int().to(dev), table.to(dev), scale=3.5, positions=at.int().to(dev), position_table=pos.to(dev))
+        torch.testing.assert_close(got.cpu(), table.float()[ids] * 3.5 + pos.float()[at], atol=1e-6, rtol=1e-6)
+        # norm of the output + residual sum, from a tensor and from partial sums
+        h, delta, w = rnd(T, dim), rnd(T, dim).to(dtype), 1.0 + 0.1 * rnd(dim)
+        want = h + plain.norm_one_plus(delta.double(), (w - 1.0).double(), 1e-5).float()
+        hh = h.clone().to(dev)
+        rows = ops.norm_add(hh, delta.to(dev), w.to(dev), 1e-5, out_dtype=dtype)
+        torch.testing.assert_close(hh.cpu(), want, atol=2e-5 if dtype == torch.float32 else 3e-2, rtol=1e-5)
+        torch.testing.assert_close(rows.float().cpu(), hh.cpu().to(dtype).float(), atol=0, rtol=0)
+        parts = rnd(3, T, dim)
+        hh = h.clone().to(dev)
+        ops.norm_add(hh, parts.to(dev), w.to(dev), 1e-5, out_dtype=dtype)
+        want = h + plain.norm_one_plus(parts.sum(0).double(), (w - 1.0).double(), 1e-5).float()
+        torch.testing.assert_close(hh.cpu(), want, atol=2e-5, rtol=1e-5)
+        # clamped gate
+        hidden = 64 if dim % 4 == 0 else 50
+        gu = (2.0 * rnd(T, 2 * hidden)).to(dtype)
+        gg, uu = gu.double()[:, :hidden].clamp(max=1.25), gu.double()[:, hidden:].clamp(-1.25, 1.25)
+        want = (gg * torch.sigmoid(1.702 * gg) * (uu + 1.0)).float()
+        got = ops.glu(gu.to(dev), limit=1.25, alpha=1.702, up_offset=1.0)
+        torch.testing.assert_close(got.float().cpu(), want, **tol)
+        # the stacked projection: [q | k | v | extra], norms over whole rows, pages, sigmoid
+        H, G, dk, dv, page = 3, 1, dim // 2 if dim <= 64 else 24, 8, 4
+        n_q, n_k, n_v, n_e = H * dk, G * dk, G * dv, H * dv
+        proj, bias = rnd(T, n_q + n_k + n_v + n_e).to(dtype), 0.3 * rnd(n_q + n_k + n_v + n_e)
+        qw, kw = 1.0 + 0.2 * rnd(n_q), 1.0 + 0.2 * rnd(n_k)
+        n_pages = -(-T // page) + 2
+        slots = torch.randperm(n_pages * page, generator=g)[:T].int()
+        k_pages = torch.zeros(n_pages, G, page, dk, dtype=dtype, device=dev)
+        v_pages = torch.zeros(n_pages, G, page, dv, dtype=dtype, device=dev)
+        q, extra = ops.project_and_store(proj.to(dev), n_q=n_q, n_k=n_k, n_v=n_v, n_extra=n_e, bias=bias.to(dev), q_norm=qw.to(dev),
+                                         k_norm=kw.to(dev), eps=1e-5, k_pages=k_pages, v_pages=v_pages, slot_mapping=slots.to(dev),
+                                         page_size=page, out_dtype=dtype)
+        x = proj.double() + bias.double()
+        xq, xk, xv, xe = x.split([n_q, n_k, n_v, n_e], dim=1)
+        torch.testing.assert_close(q.float().cpu(), plain.norm_plain(xq, qw.double(), 1e-5).float(), **tol)
+        torch.testing.assert_close(extra.float().cpu(), torch.sigmoid(xe).float(), **tol)
+        sl = slots.long()
+        torch.testing.assert_close(k_pages.cpu()[sl // page, :, sl % page].float().reshape(T, n_k),
+                                   plain.norm_plain(xk, kw.double(), 1e-5).float(), **tol)
+        torch.testing.assert_close(v_pages.cpu()[sl // page, :, sl % page].float().reshape(T, n_v), xv.float(), **tol)
+        # per-head products
+        K, N = dk, 20
+        xh, wh = rnd(T, H, K).to(dtype), (rnd(H, N, K) / K ** 0.5).to(dtype)
+        got = ops.head_linear(xh.to(dev), wh.to(dev))
+        torch.testing.assert_close(got.float().cpu(), torch.einsum("thk,hnk->thn", xh.double(), wh.double()).float(), **tol)
+
+
+@pytest.mark.gpu
+def test_clamped_gate_in_the_product_epilogue():
+    """The one-kernel form (gate in the tcgen05 product's epilogue) against product + gate kernel."""
+    from torchllms_b200.kernels import get_ops
+    ops = get_ops()
+    g = torch.Generator().manual_seed(8)
+    for M, K, hidden in ((1, 256, 128), (8, 4096, 1024), (37, 512, 192), (64, 1024, 2048)):
+        x = torch.randn(M, K, generator=g).to(torch.bfloat16).cuda()
+        w = (torch.randn(2 * hidden, K, generator=g) * (2.0 / K ** 0.5)).to(torch.bfloat16).cuda()
+        two = ops.glu(ops.linear(x, w, partials_ok=True), out_dtype=torch.bfloat16, limit=1.5, alpha=1.702, up_offset=1.0)
+        one = ops.gemm_gated_clamped(x, w, 1.5, 1.702, 1.0)
+        ops.check_status()
+        torch.testing.assert_close(one.float(), two.float(), atol=2e-2, rtol=2e-2)
+        gu = x.double() @ w.double().T
+        gg, uu = gu[:, :hidden].clamp(max=1.5), gu[:, hidden:].clamp(-1.5, 1.5)
+        torch.testing.assert_close(one.double(), gg * torch.sigmoid(1.702 * gg) * (uu + 1.0), atol=3e-2, rtol=3e-2)

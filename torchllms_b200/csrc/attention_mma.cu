@@ -115,8 +115,11 @@ __global__ void __launch_bounds__(NT, KEY_SPLIT ? 4 : 2) attention_mma_kernel(co
     const int qs = p.q_start[b];
     const int ql = p.q_start[b + 1] - qs;
     const int kl = p.kv_len[b];
-    const int tile = blockIdx.x / p.n_splits;
-    const int split = blockIdx.x - tile * p.n_splits;
+    // (prompt portions in the extended form: the last query tiles, which see the most keys, start first,
+    // so that the short walks of a portion's first tiles fill the end of the launch)
+    const int tile = (EXT && !KEY_SPLIT) ? (int)(gridDim.x / p.n_splits) - 1 - (int)(blockIdx.x / p.n_splits)
+                                         : (int)(blockIdx.x / p.n_splits);
+    const int split = blockIdx.x % p.n_splits;
     const int tokens_per_cta = KEY_SPLIT ? p.tpw : p.tpw * NW;
     const int tok0 = tile * tokens_per_cta;
     if (tok0 >= ql) return;

@@ -254,7 +254,7 @@ def adapt_tensors(cfg: NagolixConfig, found: Dict[str, LazyTensor]) -> Dict[str,
     return out
 
 
-def tensor_shapes(cfg: NagolixConfig, bias_rows: int = 16) -> Iterator[Tuple[str, Tuple[int, ...], str]]:
+def tensor_shapes(cfg: NagolixConfig, bias_rows: int = 32) -> Iterator[Tuple[str, Tuple[int, ...], str]]:
     """``(checkpoint name, shape, init)`` of every tensor, in the order random weights are drawn in."""
     d = cfg.dim
     yield "embed", (cfg.vocab_size, d), "embed"
@@ -291,7 +291,7 @@ def tensor_shapes(cfg: NagolixConfig, bias_rows: int = 16) -> Iterator[Tuple[str
 
 
 def random_tensors(cfg: NagolixConfig, seed: int, *, device="cpu", dtype: torch.dtype = torch.float32,
-                   bias_rows: int = 16) -> Iterator[Tuple[str, torch.Tensor]]:
+                   bias_rows: int = 32) -> Iterator[Tuple[str, torch.Tensor]]:
     """Seeded random weights under the checkpoint's names (one generator, one order, drawn in
     float32, then cast): matrices ``N(0, 1/fan_in)``, the table's rows of unit size over the
     embedding's scale, norm weights around zero, gains around one."""
