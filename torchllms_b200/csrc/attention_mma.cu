@@ -21,7 +21,8 @@
 // instantiated size, the tiles' spare columns zero-filled), one stored vector read as key and as
 // value (the value tile is the key tile), a window that keeps a request's first keys visible (they
 // are walked as tiles of their own ahead of the window's), a bias by bucketed distance added to the
-// scaled score, and an output gate per head or per element.
+// scaled score, and an output gate per head or per element; and it multiplies probabilities as three
+// bfloat16 terms, which add up to the float32 probability exactly.
 #include "common.cuh"
 #include <limits.h>
 #include <math.h>
@@ -368,15 +369,24 @@ __global__ void __launch_bounds__(NT, KEY_SPLIT ? 4 : 2) attention_mma_kernel(co
             // it: rounding probabilities to 8 bits would depend on the running maximum, hence
             // on how the keys fall into tiles and the prompt into steps.
 #pragma unroll
+            // The extended form serves designs that ask for 32-bit attention weights: there a third term takes
+            // what the first two leave, and the three bfloat16 numbers (8 + 8 + 8 bits) add up to the float32
+            // probability exactly, so the product is the one of float32 weights with bfloat16 values.
             for (int kk = 0; kk < KG; ++kk) {
-                unsigned ph[4], pl[4];
+                unsigned ph[4], pl[4], pt[4];
 #pragma unroll
                 for (int r = 0; r < 4; ++r) {
                     const float a = s[2 * kk + (r >> 1)][(r & 1) * 2], c = s[2 * kk + (r >> 1)][(r & 1) * 2 + 1];
                     const __nv_bfloat162 hi = __floats2bfloat162_rn(a, c);
                     const float2 back = __bfloat1622float2(hi);
                     ph[r] = *reinterpret_cast<const unsigned*>(&hi);
-                    pl[r] = pack_bf16(a - back.x, c - back.y);
+                    const float ra = a - back.x, rc = c - back.y;
+                    const __nv_bfloat162 mid = __floats2bfloat162_rn(ra, rc);
+                    pl[r] = *reinterpret_cast<const unsigned*>(&mid);
+                    if (EXT) {
+                        const float2 back2 = __bfloat1622float2(mid);
+                        pt[r] = pack_bf16(ra - back2.x, rc - back2.y);
+                    }
                 }
 #pragma unroll
                 for (int dp = 0; dp < HD / 16; ++dp) {
@@ -388,6 +398,10 @@ __global__ void __launch_bounds__(NT, KEY_SPLIT ? 4 : 2) attention_mma_kernel(co
                     mma_bf16(o[2 * dp + 1], ph, vf[2], vf[3]);
                     mma_bf16(o[2 * dp], pl, vf[0], vf[1]);
                     mma_bf16(o[2 * dp + 1], pl, vf[2], vf[3]);
+                    if (EXT) {
+                        mma_bf16(o[2 * dp], pt, vf[0], vf[1]);
+                        mma_bf16(o[2 * dp + 1], pt, vf[2], vf[3]);
+                    }
                 }
             }
         }
