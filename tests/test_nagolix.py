@@ -442,3 +442,27 @@ def test_clamped_gate_in_the_product_epilogue():
         gu = x.double() @ w.double().T
         gg, uu = gu[:, :hidden].clamp(max=1.5), gu[:, hidden:].clamp(-1.5, 1.5)
         torch.testing.assert_close(one.double(), gg * torch.sigmoid(1.702 * gg) * (uu + 1.0), atol=3e-2, rtol=3e-2)
+
+
+@pytest.mark.gpu
+def test_chat_command_line_in_token_ids(tmp_path, monkeypatch, capsys):
+    """The chat program on a folder of this architecture (no tokenizer: it chats in token ids), with a
+    longest sequence asked for that the learned position table cannot give."""
+    from torchllms_b200.inference import chat
+    cfg, tensors, folder, _page = nc.case_folder(tmp_path, "mixed")
+    lines = iter(["5 17 3", "8"])
+
+    def fake_input(_prompt=""):
+        try:
+            return next(lines)
+        except StopIteration:
+            raise EOFError
+    monkeypatch.setattr("builtins.input", fake_input)
+    chat.main(["--ckpt_paths", str(folder), "--precision", "float32", "--max_new_tokens", "4", "--max_len", "4096"])
+    said = [l for l in capsys.readouterr().out.splitlines() if l.startswith("[assistant]: ")]
+    assert len(said) == 2
+    first = [int(t) for t in said[0].split(": ")[1].split()]
+    seq = [5, 17, 3]
+    for _ in range(4):
+        seq.append(int(torch.argmax(plain.forward(cfg, tensors, seq)[-1])))
+    assert first == seq[3:]

@@ -57,11 +57,11 @@ class TorchOps:
     def check_attention_sizes(self, n_heads, n_kv_heads, head_dim, dtype, v_head_dim=None):
         assert n_heads % n_kv_heads == 0 and head_dim > 0
 
-    def embed(self, token_ids, table, scale=1.0, positions=None, position_table=None):
+    def embed(self, token_ids, table, scale=1.0, positions=None, position_table=None, rows_dtype=None):
         h = table[token_ids.long()].float() * np.float32(scale)
         if position_table is not None:
             h = h + position_table[positions.long()].float()
-        return h
+        return h if rows_dtype is None else (h, self.stream_rows(h, rows_dtype))
 
     def stream_rows(self, h, dtype):
         return h if dtype == torch.float32 else h.to(dtype)

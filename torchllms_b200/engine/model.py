@@ -83,12 +83,17 @@ class Model:
     # ----------------------------------------------------------------- forward
     def forward(self, ctx, views: Sequence) -> Optional[torch.Tensor]:
         """Run the step's tokens; returns float32 logits ``[n_wanted, vocab]`` or ``None``."""
-        if self.position_table is None and self.spec.embedding_scale == 1.0:
-            h = self.ops.embed(ctx.token_ids, self.embedding)
+        first = self.blocks[self.spec.run_order[0].layer] if self.spec.run_order else None
+        if self.position_table is None and self.spec.embedding_scale == 1.0 and not getattr(first, "reads_stream", False):
+            residual = Residual(self.ops.embed(ctx.token_ids, self.embedding))
+        elif getattr(first, "reads_stream", False):
+            # the first layer reads the stream itself: the embedding's kernel leaves it in the activation dtype too
+            h, rows = self.ops.embed(ctx.token_ids, self.embedding, scale=self.spec.embedding_scale,
+                                     positions=ctx.positions, position_table=self.position_table, rows_dtype=self.dtype)
+            residual = Residual(h, rows=rows)
         else:
-            h = self.ops.embed(ctx.token_ids, self.embedding, scale=self.spec.embedding_scale,
-                               positions=ctx.positions, position_table=self.position_table)
-        residual = Residual(h)
+            residual = Residual(self.ops.embed(ctx.token_ids, self.embedding, scale=self.spec.embedding_scale,
+                                               positions=ctx.positions, position_table=self.position_table))
         for i, run in enumerate(self.spec.run_order):
             self.blocks[run.layer].forward(residual, ctx, views[i])
         if ctx.n_want == 0:

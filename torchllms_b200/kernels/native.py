@@ -194,15 +194,22 @@ class NativeOps:
     # ------------------------------------------------------------ elementwise
     @_timed
     def embed(self, token_ids: torch.Tensor, table: torch.Tensor, scale: float = 1.0,
-              positions: Optional[torch.Tensor] = None, position_table: Optional[torch.Tensor] = None) -> torch.Tensor:
+              positions: Optional[torch.Tensor] = None, position_table: Optional[torch.Tensor] = None,
+              rows_dtype: Optional[torch.dtype] = None):
         """``table[ids]`` as the float32 stream; with ``scale`` and a learned ``position_table``:
-        ``table[ids] * scale + position_table[positions]``."""
+        ``table[ids] * scale + position_table[positions]``.  With ``rows_dtype`` the result is
+        ``(stream, the stream in that dtype)``: a first layer that reads the stream itself gets its
+        input from the same kernel (the stream itself for float32)."""
         _cuda_contig(token_ids, "token_ids", torch.int32)
         _cuda_contig(table, "embedding table")
         _need(table.dtype in _DT and table.dim() == 2, "embedding table must be a float32/bfloat16 matrix")
         n, (vocab, dim) = token_ids.numel(), table.shape
         out = torch.empty((n, dim), dtype=torch.float32, device=table.device)
-        if position_table is not None or scale != 1.0:
+        if position_table is not None or scale != 1.0 or rows_dtype is not None:
+            rows = None
+            if rows_dtype is not None and rows_dtype != torch.float32:
+                _need(rows_dtype == torch.bfloat16, f"embed: rows dtype {rows_dtype} unsupported")
+                rows = torch.empty((n, dim), dtype=rows_dtype, device=table.device)
             if position_table is not None:
                 _cuda_contig(position_table, "position table", table.dtype)
                 _cuda_contig(positions, "positions", torch.int32)
@@ -210,10 +217,12 @@ class NativeOps:
                       "position table must be [positions, width], with one position per token")
             rc = self._lib("sublayer").tl_embed_positions(
                 _ptr(token_ids), _ptr(positions if position_table is not None else None), _ptr(table), _ptr(position_table),
-                _DT[table.dtype], ctypes.c_float(scale), _ptr(out), _ptr(None), n, dim, vocab,
+                _DT[table.dtype], ctypes.c_float(scale), _ptr(out), _ptr(rows), n, dim, vocab,
                 0 if position_table is None else position_table.shape[0], _stream())
             _check(rc, "embed_positions")
             self.launches += 1
+            if rows_dtype is not None:
+                return out, (out if rows is None else rows)
             return out
         rc = self._lib("elementwise").tl_embed(_ptr(token_ids), _ptr(table), _DT[table.dtype], _ptr(out),
                                               n, dim, vocab, _stream())

@@ -74,6 +74,8 @@ class OutputNormBlock(Block):
     The sum is taken by the norm's own kernel (``Norm.fold_normed``), which also leaves the new
     stream in the activation dtype for the next reader, so nothing is pending between sublayers."""
 
+    reads_stream = True      # its first sublayer takes the stream as it is: whoever makes the stream may leave ``Residual.rows``
+
     def __init__(self, env: BuildEnv, *, mixer: PartSpec, feed_forward: Optional[PartSpec],
                  mixer_norm: PartSpec, ffn_norm: Optional[PartSpec],
                  mixer_prefix: str, ffn_prefix: str, mixer_norm_prefix: str, ffn_norm_prefix: str):
