@@ -555,7 +555,8 @@ Plan make_plan(int n_seqs, int n_heads, int n_kv_heads, int max_q_len, int max_k
         // that makes (waves / s), the time in units of one unsplit CTA, smallest, charging each
         // split a little for its partial results and the merge.
         const long long base = (long long)pl.n_q_tiles * n_kv_heads * pl.n_gchunks * n_seqs;
-        int most = max_kv_len / MIN_SPLIT;
+        // (behind a window the keys are few: a split may be as short as one tile)
+        int most = max_kv_len / (window > 0 ? BN : MIN_SPLIT);
         if (most > MERGE_MAX_SPLITS) most = MERGE_MAX_SPLITS;
         if (most > 64) most = 64;
         double best = 1e30;

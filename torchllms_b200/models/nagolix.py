@@ -67,7 +67,7 @@ class MixerConfig:
                       window=require_key(mask, "size", int, f"{where}.mask"))
         if kind == "attention":
             return cls(**common, keep_first=typed_value(mask.get("keep_first", 0), "mask.keep_first", int, where),
-                       kv_heads=require_key(raw, "kv_heads", int, where),
+                       kv_heads=typed_value(raw.get("kv_heads", common["heads"]), "kv_heads", int, where),
                        bias_max=require_key(raw, "bias_max", float, where))
         if kind == "latent_attention":
             kv_from = raw.get("kv_from")
