@@ -425,7 +425,10 @@ class NativeOps:
         N = w.shape[1]
         if x.dtype == torch.bfloat16 and T > 64:
             # prompt portions: the library's batched product, as linear() does for so many rows
-            return torch.bmm(x.transpose(0, 1), w.transpose(1, 2)).transpose(0, 1).contiguous()
+            # (heads are the batch: inputs and result are read and written in place through their strides)
+            out = torch.empty((T, H, N), dtype=x.dtype, device=x.device)
+            torch.bmm(x.transpose(0, 1), w.transpose(1, 2), out=out.transpose(0, 1))
+            return out
         out = torch.empty((T, H, N), dtype=x.dtype, device=x.device)
         _check(self._lib("gemm_simt").tl_head_linear(_ptr(x), _ptr(w), _ptr(out), _DT[x.dtype], T, H, N, K, _stream()), "head_linear")
         self.launches += 1
