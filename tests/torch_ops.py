@@ -66,13 +66,132 @@ class TorchOps:
     def stream_rows(self, h, dtype):
         return h if dtype == torch.float32 else h.to(dtype)
 
-    def norm_add(self, h, delta, weight, eps, out_dtype):
-        """h += delta / sqrt(mean(delta^2) + eps) * weight (in place, float32); the new rows in out_dtype."""
+    def norm_add(self, h, delta, weight, eps, out_dtype, then_weight=None, then_eps=0.0):
+        """h += delta / sqrt(mean(delta^2) + eps) * weight (in place, float32); the new rows in out_dtype,
+        or, with then_weight, their RMS norm under that weight."""
         if isinstance(delta, PendingProduct):
             delta = delta.take(self)
         d = delta.float().sum(0) if delta.dim() == 3 else delta.float()
         h += d * torch.rsqrt(d.pow(2).mean(-1, keepdim=True) + eps) * weight
+        if then_weight is not None:
+            return (h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + then_eps) * then_weight).to(out_dtype)
         return self.stream_rows(h, out_dtype)
+
+    def depth_mix(self, history, coef, n, out):
+        """out = sum_j coef[j] * history[j] over the first n levels (float32)."""
+        out.copy_((history[:n] * coef[:n, None, None]).sum(0))
+        return out
+
+    @staticmethod
+    def _act(x, kind):
+        if kind == "relu2":
+            return torch.relu(x) ** 2
+        if kind == "silu":
+            return x * torch.sigmoid(x)
+        if kind == "gelu_tanh":
+            return 0.5 * x * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (x + 0.044715 * x ** 3)))
+        raise ValueError(kind)
+
+    def activation(self, x, kind, out_dtype=None):
+        out_dtype = out_dtype or x.dtype
+        x = x.float().sum(0) if x.dim() == 3 else x.float()
+        return self._act(x, kind).to(out_dtype)
+
+    def gated_act(self, gate_up, activation, out_dtype=None):
+        out_dtype = out_dtype or gate_up.dtype
+        if gate_up.dim() == 3:
+            gate_up = gate_up.float().sum(0)
+        hidden = gate_up.shape[1] // 2
+        return (self._act(gate_up[:, :hidden].float(), activation) * gate_up[:, hidden:].float()).to(out_dtype)
+
+    def linear_gated_act(self, x, w_gate_up, *, activation):
+        return self.gated_act(self.linear(x, w_gate_up, partials_ok=True), activation, out_dtype=x.dtype)
+
+    def rope_store(self, proj, positions, table, *, n_q_heads, n_k_heads, n_v_heads, head_dim, v_head_dim, rot_dims,
+                   interleaved, n_extra, k_pages, v_pages, slot_mapping, page_size, out_dtype):
+        """A row of proj is [q heads | k heads | v heads | extra]: the first rot_dims coordinates of every q
+        and k head rotated by the position's angles, k and v written to their pages, sigmoid of the extra
+        columns."""
+        x = proj.float().sum(0) if proj.dim() == 3 else proj.float()
+        T = x.shape[0]
+        nq, nk, nv = n_q_heads * head_dim, n_k_heads * head_dim, n_v_heads * v_head_dim
+        assert x.shape[1] == nq + nk + nv + n_extra
+        q, k, v, e = x.split([nq, nk, nv, n_extra], dim=1)
+        cs = table[positions.long()][:, None, :rot_dims // 2]        # [T, 1, rot/2, 2]
+
+        def turn(y, heads):
+            y = y.reshape(T, heads, head_dim).clone()
+            if rot_dims:
+                r = y[..., :rot_dims]
+                a, b = (r[..., 0::2], r[..., 1::2]) if interleaved else (r[..., :rot_dims // 2], r[..., rot_dims // 2:])
+                ya, yb = a * cs[..., 0] - b * cs[..., 1], b * cs[..., 0] + a * cs[..., 1]
+                if interleaved:
+                    y[..., 0:rot_dims:2], y[..., 1:rot_dims:2] = ya, yb
+                else:
+                    y[..., :rot_dims // 2], y[..., rot_dims // 2:rot_dims] = ya, yb
+            return y
+
+        q = turn(q, n_q_heads)
+        if k_pages is not None and n_k_heads:
+            sm = slot_mapping.long()
+            page, slot = sm // page_size, sm % page_size
+            k_pages[page, :, slot] = turn(k, n_k_heads).to(k_pages.dtype)
+            v_pages[page, :, slot] = v.reshape(T, n_v_heads, v_head_dim).to(v_pages.dtype)
+        return q.to(out_dtype).contiguous(), (torch.sigmoid(e).to(out_dtype).contiguous() if n_extra else None)
+
+    def differential_combine(self, maps, lam, *, eps, out_scale, gate, out_dtype):
+        """maps [T, 2 H, dv], map-major: (a1 - lam a2) / sqrt(mean(.^2) + eps) * out_scale * gate[T, H]."""
+        T, H2, dv = maps.shape
+        a = maps.float().view(T, 2, H2 // 2, dv)
+        o = a[:, 0] - np.float32(lam) * a[:, 1]
+        o = o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + eps) * np.float32(out_scale)
+        if gate is not None:
+            o = o * gate.float()[:, :, None]
+        return o.reshape(T, -1).to(out_dtype).contiguous()
+
+    def mingru_scan(self, proj, bias, state, q_start, state_slot, fresh, *, n_seqs, max_q_len, out_dtype):
+        """proj [T, 3 W] = [z | u | g] (+ bias): S = (1 - sigmoid(z)) S + sigmoid(z) c(u), out = S * silu(g);
+        every request's state row is read (zero for a fresh request) and left updated."""
+        x = (proj.float().sum(0) if proj.dim() == 3 else proj.float()) + bias
+        W = x.shape[1] // 3
+        z, u, g = torch.sigmoid(x[:, :W]), x[:, W:2 * W], x[:, 2 * W:]
+        cand = torch.where(u >= 0, u + 0.5, torch.sigmoid(u))
+        og = g * torch.sigmoid(g)
+        out = torch.empty((x.shape[0], W), dtype=torch.float32, device=x.device)
+        qs = q_start.tolist()
+        for b in range(n_seqs):
+            slot = int(state_slot[b])
+            s = torch.zeros(W, device=x.device) if int(fresh[b]) else state[slot].clone()
+            for t in range(qs[b], qs[b + 1]):
+                s = (1.0 - z[t]) * s + z[t] * cand[t]
+                out[t] = s * og[t]
+            state[slot] = s
+        return out.to(out_dtype)
+
+    def moe_route(self, x, w_router, correction, *, n_experts, top, scale, renormalize, shared_gate):
+        z = x.float() @ w_router.t()
+        s = torch.softmax(z[:, :n_experts], dim=-1)
+        choice = s if correction is None else s + correction
+        chosen = torch.topk(choice, top, dim=-1).indices
+        w = torch.gather(s, 1, chosen)
+        if renormalize:
+            w = w / w.sum(-1, keepdim=True)
+        gate = torch.sigmoid(z[:, n_experts]).contiguous() if shared_gate else None
+        return chosen.to(torch.int32).contiguous(), (w * np.float32(scale)).contiguous(), gate
+
+    def moe_experts(self, x, chosen, weights, w_up, w_down, *, activation, shared=None, shared_gate=None):
+        T, top = chosen.shape
+        out = torch.zeros((T, w_down.shape[1]), dtype=torch.float32, device=x.device)
+        for k in range(top):
+            for e in chosen[:, k].unique().tolist():
+                rows = (chosen[:, k] == e).nonzero().flatten()
+                u = self._act(x[rows].float() @ w_up[e].float().t(), activation).to(x.dtype)
+                y = (u.float() @ w_down[e].float().t()).to(x.dtype)
+                out[rows] += weights[rows, k:k + 1] * y.float()
+        if shared is not None:
+            sh = shared.float().sum(0) if shared.dim() == 3 else shared.float()
+            out += sh if shared_gate is None else sh * shared_gate[:, None]
+        return out.to(x.dtype)
 
     def glu(self, gate_up, out_dtype=None, *, limit, alpha, up_offset):
         out_dtype = out_dtype or gate_up.dtype
@@ -210,14 +329,16 @@ class TorchOps:
 
     def paged_attention(self, q, k_pages, v_pages, block_table, q_start, kv_len, *, n_seqs, max_q_len,
                         max_kv_len, scale, window, page_size, allow_split=True, impl="auto", n_tokens=None, out=None,
-                        keep_first=0, distance_bias=None, distance_buckets=None, gate=None):
+                        keep_first=0, distance_bias=None, distance_buckets=None, gate=None, n_v_heads=None,
+                        out_dtype=None):
         T, H, hd = q.shape
         KV = k_pages.shape[1]
         group = H // KV
-        if keep_first or distance_bias is not None or gate is not None or v_pages.shape[3] != hd:
-            assert out is None and n_tokens is None
+        if keep_first or distance_bias is not None or gate is not None or v_pages.shape[3] != hd \
+                or v_pages.shape[1] != KV or out_dtype not in (None, q.dtype):
+            assert out is None and n_tokens is None and (n_v_heads or KV) == v_pages.shape[1]
             return self._attention_general(q, k_pages, v_pages, block_table, q_start, kv_len, n_seqs, scale, window,
-                                           page_size, keep_first, distance_bias, distance_buckets, gate)
+                                           page_size, keep_first, distance_bias, distance_buckets, gate, out_dtype)
         # the same contract as the kernels' front end: the step's bounds cover its requests and fit the table
         assert block_table.shape[1] * page_size >= max_kv_len, "block_table is too narrow for max_kv_len"
         assert int(kv_len[:n_seqs].max()) <= max_kv_len and n_seqs <= block_table.shape[0]
@@ -246,14 +367,14 @@ class TorchOps:
         return out
 
     def _attention_general(self, q, k_pages, v_pages, block_table, q_start, kv_len, n_seqs, scale, window, page_size,
-                           keep_first, distance_bias, distance_buckets, gate):
+                           keep_first, distance_bias, distance_buckets, gate, out_dtype=None):
         """Everything the general kernel can do, key by visible key: kept first tokens behind a
         window, a bias by bucketed distance, values of another size, an output gate per head
         ([T, H]) or per element ([T, H * dv])."""
         T, H, hd = q.shape
-        KV, dv = k_pages.shape[1], v_pages.shape[3]
+        KV, dv, VH = k_pages.shape[1], v_pages.shape[3], v_pages.shape[1]
         group = H // KV
-        out = torch.zeros((T, H, dv), dtype=q.dtype, device=q.device)
+        out = torch.zeros((T, H, dv), dtype=out_dtype or q.dtype, device=q.device)
         qs, kl = q_start.tolist(), kv_len.tolist()
         for b in range(n_seqs):
             ql, L = qs[b + 1] - qs[b], kl[b]
@@ -273,11 +394,11 @@ class TorchOps:
                 s = (qq[:, h] @ k[:, h // group].T) * scale
                 if distance_bias is not None:
                     s = s + distance_bias[distance_buckets[dist.clamp(min=0)].long(), h]
-                o = torch.softmax(s.masked_fill(hidden, float("-inf")), -1) @ v[:, h // group]
+                o = torch.softmax(s.masked_fill(hidden, float("-inf")), -1) @ v[:, (h // group) % VH]
                 if gate is not None:
                     g = gate[qs[b]:qs[b + 1]].float()
                     o = o * (g[:, h:h + 1] if gate.shape[1] == H else g.view(ql, H, dv)[:, h])
-                out[qs[b]:qs[b + 1], h] = o.to(q.dtype)
+                out[qs[b]:qs[b + 1], h] = o.to(out.dtype)
         return out
 
     def sample(self, logits, temperature=None, top_k=None, row_keys=None):

@@ -99,7 +99,7 @@ class RunCacheView:
     """What one run of a mixer sees of the cache during a step."""
 
     k_pages: Optional[torch.Tensor]      # [pages, kv_heads, page_size, head_dim]
-    v_pages: Optional[torch.Tensor]      # [pages, kv_heads, page_size, value_dim]; None where only keys are stored
+    v_pages: Optional[torch.Tensor]      # [pages, value_heads, page_size, value_dim]; None where only keys are stored
     block_table: Optional[torch.Tensor]  # [n_seqs, max_blocks] int32, FREED where no page
     slot_mapping: Optional[torch.Tensor]  # [n_tokens] int32: page * page_size + offset
     page_size: int
@@ -120,7 +120,8 @@ class CacheGroup:
         self.allocator = PageAllocator(n_pages)
         shape = (len(runs), n_pages, need.n_kv_heads, page_size)
         self.k_pages = torch.zeros(shape + (need.head_dim,), dtype=dtype, device=device)
-        self.v_pages = torch.zeros(shape + (need.value_dim,), dtype=dtype, device=device) if need.value_dim else None
+        v_shape = (len(runs), n_pages, need.value_heads, page_size, need.value_dim)
+        self.v_pages = torch.zeros(v_shape, dtype=dtype, device=device) if need.value_dim else None
         self.run_index = {run: i for i, run in enumerate(self.runs)}
         # blocks that hold the first tokens a window keeps: never given back while the request lives
         self.kept_blocks = -(-need.keep_first // page_size) if need.kind == "window" else 0

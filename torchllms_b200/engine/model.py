@@ -14,7 +14,7 @@ from typing import Dict, List, Mapping, Optional, Sequence, Tuple
 
 import torch
 
-from ..parts import attention, block, ffn, latent_attention, norm, rope  # noqa: F401  (register the built-in parts)
+from ..parts import attention, block, ffn, latent_attention, moe, norm, recurrent, rope  # noqa: F401  (register the built-in parts)
 from ..parts.base import BLOCKS, NORMS, BuildEnv, CacheNeed, Residual, StateNeed, as_compute
 from ..parts.spec import ModelSpec
 from ..weights.loader import ExpectedTensor
@@ -81,10 +81,33 @@ class Model:
                 for run in self.spec.run_order]
 
     # ----------------------------------------------------------------- forward
+    def _residual_with_history(self, ctx) -> Residual:
+        """Level 0 holds the embedding output, one more level every layer run, and a last one for
+        what leaves the last run.  The stream of the first run starts as a copy of level 0."""
+        h0 = self.ops.embed(ctx.token_ids, self.embedding, scale=self.spec.embedding_scale,
+                            positions=ctx.positions if self.position_table is not None else None,
+                            position_table=self.position_table)
+        history = torch.empty((len(self.spec.run_order) + 2, *h0.shape), dtype=torch.float32, device=h0.device)
+        history[0].copy_(h0)
+        history[1].copy_(h0)
+        return Residual(history[1], history=history)
+
+    def _next_level(self, residual: Residual) -> None:
+        """A run is finished and left its result in the level being written; the next run's
+        stream starts from it."""
+        if residual.delta is not None:
+            raise RuntimeError("a block of a model that keeps its history must not leave a sum pending")
+        residual.level += 1
+        nxt = residual.history[residual.level + 1]
+        nxt.copy_(residual.h)
+        residual.h, residual.rows = nxt, None
+
     def forward(self, ctx, views: Sequence) -> Optional[torch.Tensor]:
         """Run the step's tokens; returns float32 logits ``[n_wanted, vocab]`` or ``None``."""
         first = self.blocks[self.spec.run_order[0].layer] if self.spec.run_order else None
-        if self.position_table is None and self.spec.embedding_scale == 1.0 and not getattr(first, "reads_stream", False):
+        if self.spec.keeps_history:
+            residual = self._residual_with_history(ctx)
+        elif self.position_table is None and self.spec.embedding_scale == 1.0 and not getattr(first, "reads_stream", False):
             residual = Residual(self.ops.embed(ctx.token_ids, self.embedding))
         elif getattr(first, "reads_stream", False):
             # the first layer reads the stream itself: the embedding's kernel leaves it in the activation dtype too
@@ -96,6 +119,8 @@ class Model:
                                                positions=ctx.positions, position_table=self.position_table))
         for i, run in enumerate(self.spec.run_order):
             self.blocks[run.layer].forward(residual, ctx, views[i])
+            if residual.history is not None and residual.level != i + 1:
+                self._next_level(residual)      # a block that reads no earlier results: the stream passes as it is
         if ctx.n_want == 0:
             return None
         x = self.final_norm.forward(residual, rows=ctx.want_rows)

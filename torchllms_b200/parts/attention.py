@@ -20,6 +20,7 @@ import torch
 from ..kernels.lazy import PendingProduct
 from ..weights.loader import ExpectedTensor
 from .base import (POSITION_ENCODINGS, BuildEnv, CacheNeed, Mixer, as_compute, register_mixer)
+from .rope import precise_rotary_table
 from .spec import PartSpec
 
 
@@ -218,3 +219,108 @@ class GatedBiasedAttention(Mixer):
             window=self.window, page_size=cache.page_size, keep_first=self.keep_first,
             distance_bias=self.distance_bias, distance_buckets=self.buckets, gate=gate, impl="auto")
         return PendingProduct(o.view(o.shape[0], self.n_heads * self.v_head_dim), self.wo)
+
+
+@register_mixer("differential_attention")
+class DifferentialAttention(Mixer):
+    """Grouped-query attention with two softmax maps per head over one set of values, combined by
+    subtraction:
+
+    * ``wq`` has ``n_heads * 2 * head_dim`` rows and ``wk`` ``n_kv_heads * 2 * head_dim``, head by
+      head as ``[map 1, map 2]``; ``wv`` has ``n_kv_heads * v_head_dim`` rows; no biases;
+    * rotary positions on the first ``rot_dims`` coordinates of every map of q and k (``rot_pairing``
+      ``"half"``: coordinate ``i`` with ``i + rot_dims / 2``), angles ``p * rot_base^(-2i/rot_dims) /
+      rot_factor``; keys are stored rotated;
+    * each map is causal softmax attention with ``score = q . k * scale``;
+    * ``o = a1 - lambda a2`` with ``lambda = exp(lambda_q1 . lambda_k1) - exp(lambda_q2 . lambda_k2)
+      + lambda_init`` (four stored vectors of ``head_dim``, one number for the layer), then
+      ``o / sqrt(mean(o^2) + norm_eps)`` over the head's values, times ``1 - lambda_init``;
+    * with ``gated``, head ``h`` is multiplied by ``sigmoid(wg x)_h`` (``wg [n_heads, dim]``);
+    * ``wo`` on the concatenated heads.  ``own_kv=False``: a run that reads another run's keys
+      and values has neither ``wk`` nor ``wv``.
+
+    The cache holds ``2 * n_kv_heads`` key heads (map-major: all first maps, then all second
+    maps, the order q is projected in too, so that each map is ordinary grouped attention) and
+    ``n_kv_heads`` value heads.  One stacked product gives q, k, v and the gate; one kernel
+    rotates, stores and takes the gate's sigmoid; the attention kernel returns both maps in
+    32-bit, and one kernel combines, normalises and gates them."""
+
+    graph_safe = True
+
+    def __init__(self, env: BuildEnv, *, dim: int, n_heads: int, n_kv_heads: int, head_dim: int, v_head_dim: int,
+                 scale: float, lambda_init: float, norm_eps: float, rot_dims: int, rot_base: float,
+                 rot_factor: float = 1.0, rot_pairing: str = "half", gated: bool = True, own_kv: bool = True):
+        if n_heads % n_kv_heads != 0:
+            raise ValueError(f"n_heads ({n_heads}) must be a multiple of n_kv_heads ({n_kv_heads})")
+        if rot_dims < 0 or rot_dims % 2 or rot_dims > head_dim:
+            raise ValueError(f"rot_dims must be even and at most head_dim ({head_dim}), got {rot_dims}")
+        if rot_pairing not in ("half", "interleaved"):
+            raise ValueError(f"rot_pairing must be 'half' or 'interleaved', got {rot_pairing!r}")
+        self.env = env
+        self.dim, self.n_heads, self.n_kv_heads = int(dim), int(n_heads), int(n_kv_heads)
+        self.head_dim, self.v_head_dim = int(head_dim), int(v_head_dim)
+        self.scale, self.lambda_init, self.norm_eps = float(scale), float(lambda_init), float(norm_eps)
+        self.rot_dims, self.rot_pairing = int(rot_dims), rot_pairing
+        self.gated, self.own_kv = bool(gated), bool(own_kv)
+        self.n_q = 2 * self.n_heads * self.head_dim
+        self.n_k = 2 * self.n_kv_heads * self.head_dim
+        self.n_v = self.n_kv_heads * self.v_head_dim
+        env.ops.check_attention_sizes(2 * self.n_heads, 2 * self.n_kv_heads, self.head_dim, env.dtype, v_head_dim=self.v_head_dim)
+        self.table = precise_rotary_table(max(self.rot_dims, 2), rot_base, rot_factor, env.max_positions).to(env.device)
+        self.lam = 0.0
+        self.w_in: Optional[torch.Tensor] = None
+        self.wo: Optional[torch.Tensor] = None
+
+    def cache_need(self) -> CacheNeed:
+        return CacheNeed("full", 2 * self.n_kv_heads, self.head_dim, None, self.v_head_dim, 0, self.n_kv_heads)
+
+    def expected_tensors(self) -> Dict[str, ExpectedTensor]:
+        out = {"wq.weight": ExpectedTensor((self.n_q, self.dim)),
+               "wo.weight": ExpectedTensor((self.dim, self.n_heads * self.v_head_dim))}
+        if self.own_kv:
+            out["wk.weight"] = ExpectedTensor((self.n_k, self.dim))
+            out["wv.weight"] = ExpectedTensor((self.n_v, self.dim))
+        for name in ("lambda_q1", "lambda_k1", "lambda_q2", "lambda_k2"):
+            out[name] = ExpectedTensor((self.head_dim,))
+        if self.gated:
+            out["wg.weight"] = ExpectedTensor((self.n_heads, self.dim))
+        return out
+
+    def _map_major(self, w: torch.Tensor, heads: int) -> torch.Tensor:
+        """Rows ``[head][map][coordinate]`` as ``[map][head][coordinate]``."""
+        return w.view(heads, 2, self.head_dim, self.dim).transpose(0, 1).reshape(2 * heads * self.head_dim, self.dim)
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        rows = [self._map_major(as_compute(tensors["wq.weight"], self.env), self.n_heads)]
+        if self.own_kv:
+            rows += [self._map_major(as_compute(tensors["wk.weight"], self.env), self.n_kv_heads),
+                     as_compute(tensors["wv.weight"], self.env)]
+        if self.gated:
+            rows.append(as_compute(tensors["wg.weight"], self.env))
+        self.w_in = torch.cat(rows).contiguous()                               # rows [wq; wk; wv; wg]
+        dots = [float((tensors[f"lambda_q{i}"].double() * tensors[f"lambda_k{i}"].double()).sum()) for i in (1, 2)]
+        self.lam = math.exp(dots[0]) - math.exp(dots[1]) + self.lambda_init
+        self.wo = as_compute(tensors["wo.weight"], self.env)
+
+    def weight_bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in (self.w_in, self.wo))     # (the table is gathered by rows)
+
+    def forward(self, x: torch.Tensor, ctx, cache) -> PendingProduct:
+        ops = self.env.ops
+        H, G = self.n_heads, self.n_kv_heads
+        if cache.writes != self.own_kv:
+            raise RuntimeError("a differential attention layer owns its keys and values exactly when it projects them")
+        proj = ops.linear(x, self.w_in, partials_ok=True)
+        q, gate = ops.rope_store(
+            proj, ctx.positions, self.table, n_q_heads=2 * H, n_k_heads=2 * G if self.own_kv else 0,
+            n_v_heads=G if self.own_kv else 0, head_dim=self.head_dim, v_head_dim=self.v_head_dim, rot_dims=self.rot_dims,
+            interleaved=self.rot_pairing == "interleaved", n_extra=H if self.gated else 0,
+            k_pages=cache.k_pages if self.own_kv else None, v_pages=cache.v_pages if self.own_kv else None,
+            slot_mapping=cache.slot_mapping, page_size=cache.page_size, out_dtype=self.env.dtype)
+        maps = ops.paged_attention(
+            q, cache.k_pages, cache.v_pages, cache.block_table, ctx.q_start, ctx.kv_len, n_seqs=ctx.n_seqs,
+            max_q_len=ctx.max_q_len, max_kv_len=ctx.max_kv_len, scale=self.scale, window=None, page_size=cache.page_size,
+            n_v_heads=G, out_dtype=torch.float32)                              # [T, 2 H, v_head_dim], map-major
+        o = ops.differential_combine(maps, self.lam, eps=self.norm_eps, out_scale=1.0 - self.lambda_init, gate=gate,
+                                     out_dtype=self.env.dtype)
+        return PendingProduct(o, self.wo)

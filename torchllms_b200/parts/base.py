@@ -52,8 +52,10 @@ class CacheNeed:
     ``keep_first`` the first so many tokens of a request are read for ever and
     their pages stay).  ``v_head_dim`` is the size of a stored value when it
     differs from a key's; 0 means that nothing but keys is stored (a mixer
-    that derives keys and values from one stored vector).  Runs with equal
-    needs share one group of pages and one block table.
+    that derives keys and values from one stored vector).  ``n_v_heads`` is the number of value
+    heads when it differs from the number of key heads (key head ``j`` then goes with value head
+    ``j % n_v_heads``: several attention maps, each with keys of its own, over one set of values).
+    Runs with equal needs share one group of pages and one block table.
     """
 
     kind: str
@@ -62,6 +64,7 @@ class CacheNeed:
     window: Optional[int] = None
     v_head_dim: Optional[int] = None
     keep_first: int = 0
+    n_v_heads: Optional[int] = None
 
     def __post_init__(self):
         if self.kind not in ("full", "window"):
@@ -72,21 +75,32 @@ class CacheNeed:
             raise ValueError("keep_first is a count of tokens and goes with kind 'window' only")
         if self.v_head_dim is not None and self.v_head_dim == self.head_dim:
             object.__setattr__(self, "v_head_dim", None)      # one spelling for equal needs
+        if self.n_v_heads is not None:
+            if self.n_v_heads <= 0 or self.n_kv_heads % self.n_v_heads != 0:
+                raise ValueError(f"n_v_heads ({self.n_v_heads}) must divide n_kv_heads ({self.n_kv_heads})")
+            if self.n_v_heads == self.n_kv_heads:
+                object.__setattr__(self, "n_v_heads", None)
 
     @property
     def value_dim(self) -> int:
         """Elements of one stored value (0: none are stored)."""
         return self.head_dim if self.v_head_dim is None else self.v_head_dim
 
+    @property
+    def value_heads(self) -> int:
+        """How many heads a stored value has."""
+        return self.n_kv_heads if self.n_v_heads is None else self.n_v_heads
+
     def covering(self, other: "CacheNeed") -> "CacheNeed":
         """The need that keeps what both this one and ``other`` (a run that reads this run's cache
         through a mask of its own) will read."""
-        if (other.n_kv_heads, other.head_dim, other.value_dim) != (self.n_kv_heads, self.head_dim, self.value_dim):
+        if (other.n_kv_heads, other.head_dim, other.value_dim, other.value_heads) != \
+                (self.n_kv_heads, self.head_dim, self.value_dim, self.value_heads):
             raise ValueError("a run can read another run's cache only if both store the same vectors")
         if self.kind == "full" or other.kind == "full":
-            return CacheNeed("full", self.n_kv_heads, self.head_dim, None, self.v_head_dim, 0)
+            return CacheNeed("full", self.n_kv_heads, self.head_dim, None, self.v_head_dim, 0, self.n_v_heads)
         return CacheNeed("window", self.n_kv_heads, self.head_dim, max(self.window, other.window), self.v_head_dim,
-                         max(self.keep_first, other.keep_first))
+                         max(self.keep_first, other.keep_first), self.n_v_heads)
 
 
 @dataclass(frozen=True)
@@ -220,14 +234,22 @@ class Residual:
     ``rows`` is the stream as the activation dtype holds it, when the kernel that last wrote
     ``h`` left such a copy (a block whose sublayers read the stream itself, without a norm in
     front, takes its input from there); whoever changes ``h`` afterwards sets it to ``None``.
+
+    ``history`` is there for models whose layers read earlier layers' results
+    (``ModelSpec.keeps_history``): ``[levels, T, dim]`` float32, level 0 the embedding output,
+    level ``j`` the result of the ``j``-th layer run; ``level`` counts the finished ones, and ``h``
+    is then a view of ``history[level + 1]``, the level being written.
     """
 
-    __slots__ = ("h", "delta", "rows")
+    __slots__ = ("h", "delta", "rows", "history", "level")
 
-    def __init__(self, h: torch.Tensor, delta: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None):
+    def __init__(self, h: torch.Tensor, delta: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None,
+                 history: Optional[torch.Tensor] = None):
         self.h = h
         self.delta = delta
         self.rows = rows
+        self.history = history
+        self.level = 0
 
 
 # --------------------------------------------------------------------------- registries

@@ -118,3 +118,85 @@ class OutputNormBlock(Block):
         self.mixer_norm.fold_normed(residual, self.mixer.forward(self._input(residual), ctx, cache))
         if self.feed_forward is not None:
             self.ffn_norm.fold_normed(residual, self.feed_forward.forward(self._input(residual), ctx))
+
+
+@register_block("sandwich")
+class SandwichBlock(Block):
+    """A norm in front of each sublayer and another on its output: ``x += out_norm1(mixer(norm1(x)))``,
+    then ``x += out_norm2(ff(norm2(x)))``.  A layer may have no feed-forward.
+
+    With ``depth_inputs = n`` the layer ends in an average over depth: what goes on is
+    ``sum_j c[j] X_j`` over the first ``n`` levels of the model's history (level 0 the embedding
+    output, level ``j`` the result of the ``j``-th layer run before any averaging, the last of the
+    ``n`` this layer's own), with the coefficients in the layer's tensor ``depth_tensor``.  Such a
+    block needs a model that keeps its history (``ModelSpec.keeps_history``).
+
+    The output norm's kernel adds to the stream and, where a feed-forward follows, also takes the
+    norm in front of it, so two kernels stand between the mixer's and the feed-forward's products."""
+
+    def __init__(self, env: BuildEnv, *, mixer: PartSpec, feed_forward: Optional[PartSpec],
+                 mixer_norm: PartSpec, mixer_out_norm: PartSpec, ffn_norm: Optional[PartSpec],
+                 ffn_out_norm: Optional[PartSpec], mixer_prefix: str, ffn_prefix: str, mixer_norm_prefix: str,
+                 mixer_out_norm_prefix: str, ffn_norm_prefix: str, ffn_out_norm_prefix: str,
+                 depth_inputs: Optional[int] = None, depth_tensor: str = "depth"):
+        self.env = env
+        self.mixer = MIXERS.build(mixer, env)
+        self.mixer_norm = NORMS.build(mixer_norm, env)
+        self.mixer_out_norm = NORMS.build(mixer_out_norm, env)
+        self._subparts = [(mixer_prefix, self.mixer), (mixer_norm_prefix, self.mixer_norm),
+                          (mixer_out_norm_prefix, self.mixer_out_norm)]
+        self.feed_forward = self.ffn_norm = self.ffn_out_norm = None
+        if feed_forward is not None:
+            self.feed_forward = FEED_FORWARDS.build(feed_forward, env)
+            self.ffn_norm = NORMS.build(ffn_norm, env)
+            self.ffn_out_norm = NORMS.build(ffn_out_norm, env)
+            self._subparts += [(ffn_prefix, self.feed_forward), (ffn_norm_prefix, self.ffn_norm),
+                               (ffn_out_norm_prefix, self.ffn_out_norm)]
+        self.depth_inputs = None if depth_inputs is None else int(depth_inputs)
+        if self.depth_inputs is not None and self.depth_inputs < 1:
+            raise ValueError(f"an average over depth reads at least one level, got {depth_inputs}")
+        self.depth_tensor = depth_tensor
+        self.depth_coef: Optional[torch.Tensor] = None
+        self.graph_safe = all(sub.graph_safe for _p, sub in self._subparts)
+
+    def cache_need(self):
+        return self.mixer.cache_need()
+
+    def state_need(self):
+        return self.mixer.state_need()
+
+    def expected_tensors(self) -> Dict[str, ExpectedTensor]:
+        out: Dict[str, ExpectedTensor] = {}
+        for prefix, sub in self._subparts:
+            for name, e in sub.expected_tensors().items():
+                out[f"{prefix}.{name}"] = e
+        if self.depth_inputs is not None:
+            out[self.depth_tensor] = ExpectedTensor((self.depth_inputs,))
+        return out
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        for prefix, sub in self._subparts:
+            sub.load({name: tensors[f"{prefix}.{name}"] for name in sub.expected_tensors()})
+        if self.depth_inputs is not None:
+            self.depth_coef = tensors[self.depth_tensor].to(device=self.env.device, dtype=torch.float32).contiguous()
+
+    def weight_bytes(self) -> int:
+        return sum(sub.weight_bytes() for _p, sub in self._subparts)
+
+    def forward(self, residual: Residual, ctx, cache) -> None:
+        if residual.delta is not None:
+            raise RuntimeError("a sandwich block cannot follow a block that leaves its sum pending")
+        y = self.mixer.forward(self.mixer_norm.forward(residual), ctx, cache)
+        if self.feed_forward is None:
+            self.mixer_out_norm.fold_normed(residual, y, want_rows=False)
+        else:
+            x = self.mixer_out_norm.fold_normed(residual, y, then=self.ffn_norm)
+            self.ffn_out_norm.fold_normed(residual, self.feed_forward.forward(x, ctx), want_rows=False)
+        if self.depth_inputs is not None:
+            history, level = residual.history, residual.level
+            if history is None or self.depth_inputs != level + 2:
+                raise RuntimeError(f"this layer averages over {self.depth_inputs} levels of the model's history, "
+                                   f"but {'there is none' if history is None else f'{level + 2} exist'}")
+            nxt = history[level + 2]
+            self.env.ops.depth_mix(history, self.depth_coef, self.depth_inputs, nxt)
+            residual.h, residual.rows, residual.level = nxt, None, level + 1

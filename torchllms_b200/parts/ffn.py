@@ -80,3 +80,39 @@ class ClampedGLU(FeedForward):
     def forward(self, x: torch.Tensor, ctx) -> PendingProduct:
         y = self.env.ops.linear_glu(x, self.w_gate_up, limit=self.limit, alpha=self.alpha, up_offset=self.up_offset)
         return PendingProduct(y, self.w_down)       # the down projection is left to the norm that follows
+
+
+GATE_ACTIVATIONS = ("silu", "gelu_tanh")
+
+
+@register_feed_forward("glu")
+class GatedLinearUnit(FeedForward):
+    """Dense gated feed-forward with a choice of activation: ``down(act(gate x) * up x)``, ``act``
+    being ``silu`` or ``gelu_tanh`` (``0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3)))``).
+    Weights ``gate.weight`` and ``up.weight`` are ``[hidden, dim]``, ``down.weight`` is ``[dim, hidden]``;
+    gate and up are stacked so that one product yields both.  The activation is float32 arithmetic."""
+
+    graph_safe = True
+
+    def __init__(self, env: BuildEnv, *, dim: int, hidden: int, activation: str):
+        if activation not in GATE_ACTIVATIONS:
+            raise ValueError(f"unknown gate activation {activation!r}; known: {', '.join(GATE_ACTIVATIONS)}")
+        self.env = env
+        self.dim, self.hidden, self.activation = int(dim), int(hidden), activation
+        self.w_gate_up: Optional[torch.Tensor] = None
+        self.w_down: Optional[torch.Tensor] = None
+
+    def expected_tensors(self) -> Dict[str, ExpectedTensor]:
+        return {
+            "gate.weight": ExpectedTensor((self.hidden, self.dim)),
+            "up.weight": ExpectedTensor((self.hidden, self.dim)),
+            "down.weight": ExpectedTensor((self.dim, self.hidden)),
+        }
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        self.w_gate_up = torch.cat([as_compute(tensors["gate.weight"], self.env), as_compute(tensors["up.weight"], self.env)])
+        self.w_down = as_compute(tensors["down.weight"], self.env)
+
+    def forward(self, x: torch.Tensor, ctx) -> PendingProduct:
+        y = self.env.ops.linear_gated_act(x, self.w_gate_up, activation=self.activation)
+        return PendingProduct(y, self.w_down)       # the down projection is left to the norm that follows

@@ -1,0 +1,104 @@
+"""Feed-forward layers made of many small experts, of which every token uses a few.
+
+Routing runs on the device: a kernel takes the router's scores and picks the experts, another
+sorts the (token, expert) pairs by expert, the experts' products run as one grouped product over
+the sorted rows, and a last kernel adds up every token's weighted results.  Nothing is read back,
+so the shapes of a step's launches depend on its token count alone.
+"""
+
+from __future__ import annotations
+
+from typing import Dict, Mapping, Optional
+
+import torch
+
+from ..weights.loader import ExpectedTensor
+from .base import BuildEnv, FeedForward, as_compute, register_feed_forward
+
+EXPERT_ACTIVATIONS = ("relu2", "silu", "gelu_tanh")
+
+
+@register_feed_forward("routed_experts")
+class RoutedExperts(FeedForward):
+    """``n_experts`` feed-forwards ``down_e(act(up_e x))`` without biases; a token uses ``top`` of them.
+
+    * router logits ``z = W_router x`` and scores ``s = softmax(z)`` over all experts, in float32;
+    * the experts with the largest ``s + correction`` are chosen (``choice_correction``: a stored
+      vector ``correction`` that steers the choice and nothing else);
+    * their weights are ``s * router_scale``, divided by their sum first with ``renormalize``;
+    * with ``shared_hidden`` a shared expert of the same form runs for every token and is added,
+      multiplied by ``sigmoid(W_sg x)`` (one number per token) with ``shared_gate``.
+
+    Tensors: ``router.weight [E, dim]``, ``correction [E]``, ``experts.<e>.up.weight [hidden, dim]``,
+    ``experts.<e>.down.weight [dim, hidden]``, ``shared.up.weight``, ``shared.down.weight``,
+    ``shared.gate.weight [1, dim]``."""
+
+    graph_safe = True
+
+    def __init__(self, env: BuildEnv, *, dim: int, n_experts: int, top: int, hidden: int, activation: str = "relu2",
+                 router_scale: float = 1.0, choice_correction: bool = False, renormalize: bool = False,
+                 shared_hidden: Optional[int] = None, shared_gate: bool = False):
+        if activation not in EXPERT_ACTIVATIONS:
+            raise ValueError(f"unknown expert activation {activation!r}; known: {', '.join(EXPERT_ACTIVATIONS)}")
+        if not 0 < top <= n_experts:
+            raise ValueError(f"a token uses between 1 and {n_experts} experts, got {top}")
+        if shared_gate and not shared_hidden:
+            raise ValueError("a gate of the shared expert needs a shared expert")
+        self.env = env
+        self.dim, self.n_experts, self.top, self.hidden = int(dim), int(n_experts), int(top), int(hidden)
+        self.activation = activation
+        self.router_scale = float(router_scale)
+        self.choice_correction, self.renormalize = bool(choice_correction), bool(renormalize)
+        self.shared_hidden = None if not shared_hidden else int(shared_hidden)
+        self.shared_gate = bool(shared_gate)
+        self.w_router: Optional[torch.Tensor] = None       # float32 [E (+ 1), dim]: the gate's row rides along
+        self.correction: Optional[torch.Tensor] = None
+        self.w_up: Optional[torch.Tensor] = None           # [E, hidden, dim]
+        self.w_down: Optional[torch.Tensor] = None         # [E, dim, hidden]
+        self.w_shared_up: Optional[torch.Tensor] = None
+        self.w_shared_down: Optional[torch.Tensor] = None
+
+    def expected_tensors(self) -> Dict[str, ExpectedTensor]:
+        out = {"router.weight": ExpectedTensor((self.n_experts, self.dim))}
+        if self.choice_correction:
+            out["correction"] = ExpectedTensor((self.n_experts,))
+        for e in range(self.n_experts):
+            out[f"experts.{e}.up.weight"] = ExpectedTensor((self.hidden, self.dim))
+            out[f"experts.{e}.down.weight"] = ExpectedTensor((self.dim, self.hidden))
+        if self.shared_hidden:
+            out["shared.up.weight"] = ExpectedTensor((self.shared_hidden, self.dim))
+            out["shared.down.weight"] = ExpectedTensor((self.dim, self.shared_hidden))
+            if self.shared_gate:
+                out["shared.gate.weight"] = ExpectedTensor((1, self.dim))
+        return out
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        f32 = dict(device=self.env.device, dtype=torch.float32)
+        rows = [tensors["router.weight"].to(**f32)]
+        if self.shared_gate:
+            rows.append(tensors["shared.gate.weight"].to(**f32))
+        self.w_router = torch.cat(rows).contiguous()
+        if self.choice_correction:
+            self.correction = tensors["correction"].to(**f32).contiguous()
+        self.w_up = torch.stack([as_compute(tensors[f"experts.{e}.up.weight"], self.env) for e in range(self.n_experts)])
+        self.w_down = torch.stack([as_compute(tensors[f"experts.{e}.down.weight"], self.env) for e in range(self.n_experts)])
+        if self.shared_hidden:
+            self.w_shared_up = as_compute(tensors["shared.up.weight"], self.env)
+            self.w_shared_down = as_compute(tensors["shared.down.weight"], self.env)
+
+    def weight_bytes(self) -> int:
+        """What a step reads at most: the router, the shared expert, and ``top`` experts per token
+        (a step of few tokens leaves most experts alone; this counts all of them)."""
+        return super().weight_bytes()
+
+    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        ops = self.env.ops
+        chosen, weights, gate = ops.moe_route(x, self.w_router, self.correction, n_experts=self.n_experts, top=self.top,
+                                              scale=self.router_scale, renormalize=self.renormalize,
+                                              shared_gate=self.shared_gate)
+        shared = None
+        if self.shared_hidden:
+            u = ops.activation(ops.linear(x, self.w_shared_up, partials_ok=True), self.activation, out_dtype=self.env.dtype)
+            shared = ops.linear(u, self.w_shared_down, partials_ok=True)
+        return ops.moe_experts(x, chosen, weights, self.w_up, self.w_down, activation=self.activation,
+                               shared=shared, shared_gate=gate)

@@ -33,20 +33,23 @@ class RMSNorm(Norm):
     graph_safe = True
     can_defer = True
 
-    def __init__(self, env: BuildEnv, *, dim: int, eps: float, offset: float = 0.0):
-        """``offset``: what is added to the stored weight (1 for a weight that is kept around zero)."""
+    def __init__(self, env: BuildEnv, *, dim: int, eps: float, offset: float = 0.0, scalar: bool = False):
+        """``offset``: what is added to the stored weight (1 for a weight that is kept around zero).
+        ``scalar``: the stored weight is one number for all coordinates (a tensor without axes)."""
         self.env = env
+        self.scalar = bool(scalar)
         self.dim = int(dim)
         self.eps = float(eps)
         self.offset = float(offset)
         self.weight: Optional[torch.Tensor] = None
 
     def expected_tensors(self) -> Dict[str, ExpectedTensor]:
-        return {"weight": ExpectedTensor((self.dim,))}
+        return {"weight": ExpectedTensor(() if self.scalar else (self.dim,))}
 
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
         # Kept in 32-bit whatever the activation dtype: the kernel multiplies in 32-bit.
-        self.weight = (tensors["weight"].to(device=self.env.device, dtype=torch.float32) + self.offset).contiguous()
+        w = tensors["weight"].to(device=self.env.device, dtype=torch.float32) + self.offset
+        self.weight = (w.reshape(1).expand(self.dim) if self.scalar else w).contiguous()
 
     def forward(self, residual: Residual, rows: Optional[torch.Tensor] = None, deferred_ok: bool = False):
         ops = self.env.ops
@@ -67,10 +70,22 @@ class RMSNorm(Norm):
             residual.rows = None
         return out
 
-    def fold_normed(self, residual: Residual, delta) -> None:
+    def fold_normed(self, residual: Residual, delta, want_rows: bool = True, then: Optional["RMSNorm"] = None):
         """The norm on a sublayer's *output*: ``h += norm(delta)`` in 32-bit, in one kernel that also
         leaves the new stream in the activation dtype (``residual.rows``) for the sublayer that
-        reads it next.  ``delta`` is a tensor, float32 partial sums or a
-        :class:`~torchllms_b200.kernels.lazy.PendingProduct`."""
-        residual.rows = self.env.ops.norm_add(residual.h, delta, self.weight, self.eps, out_dtype=self.env.dtype)
+        reads it next (not with ``want_rows=False``: a reader that has a norm of its own in front).
+        ``delta`` is a tensor, float32 partial sums or a
+        :class:`~torchllms_b200.kernels.lazy.PendingProduct`.  With ``then`` (the norm in front of
+        the next reader) the same kernel also returns ``then(h)`` in the activation dtype."""
+        ops = self.env.ops
         residual.delta = None
+        if then is not None:
+            residual.rows = None
+            return ops.norm_add(residual.h, delta, self.weight, self.eps, out_dtype=self.env.dtype,
+                                then_weight=then.weight, then_eps=then.eps)
+        if not want_rows:
+            ops.norm_add(residual.h, delta, self.weight, self.eps, out_dtype=torch.float32)
+            residual.rows = None
+            return None
+        residual.rows = ops.norm_add(residual.h, delta, self.weight, self.eps, out_dtype=self.env.dtype)
+        return None

@@ -40,6 +40,8 @@ def rotary_frequencies(head_dim: int, theta: float, scaling: Optional[Mapping[st
         blended = (1 - smooth) * scaled / factor + smooth * scaled
         medium = ~(wavelen < original / high) & ~(wavelen > original / low)
         freq = torch.where(medium, blended, scaled)
+    elif rope_type == "linear":
+        freq = freq / float(scaling["factor"])         # every frequency divided by one factor
     elif rope_type != "default":
         raise ValueError(f"unknown rope_type {rope_type!r}")
     return freq
@@ -50,6 +52,15 @@ def rotary_table(freq: torch.Tensor, max_positions: int) -> torch.Tensor:
     positions = torch.arange(max_positions, dtype=freq.dtype)
     angles = torch.einsum("i,j->ij", positions, freq).float()
     return torch.stack([torch.cos(angles), torch.sin(angles)], dim=-1).contiguous()
+
+
+def precise_rotary_table(dims: int, theta: float, factor: float, max_positions: int) -> torch.Tensor:
+    """``[max_positions, dims / 2, 2]`` float32 (cos, sin) of the angles ``p * theta^(-2i/dims) / factor``,
+    the angles taken in 64-bit so that the table is exact to float32 rounding at any position."""
+    i = torch.arange(dims // 2, dtype=torch.float64)
+    freq = float(theta) ** (-2.0 * i / dims) / float(factor)
+    angles = torch.arange(max_positions, dtype=torch.float64)[:, None] * freq[None, :]
+    return torch.stack([torch.cos(angles), torch.sin(angles)], dim=-1).to(torch.float32).contiguous()
 
 
 @register_position_encoding("rope")

@@ -74,6 +74,7 @@ class ModelSpec:
     tie_head: bool = False           # the head is the embedding table; head_tensor is absent
     embedding_scale: float = 1.0     # the rows of the table enter the stream multiplied by this
     position_tensor: Optional[str] = None   # name of a learned [max_positions, dim] table added to the embedding
+    keeps_history: bool = False      # the result of every layer run stays readable by later runs (Residual.history)
 
     def __post_init__(self):
         n = len(self.layers)
