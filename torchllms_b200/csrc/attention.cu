@@ -9,6 +9,10 @@
 //   gate         the result is multiplied by a gate value, one per (token, head) or one per element
 //   v_head_dim   values of another size than keys; v_pages may be the very tensor k_pages (a mixer
 //                that attends over one stored vector as key and value)
+//   n_v_heads    fewer value heads than key heads: key head j goes with value head j % n_v_heads
+//                (several attention maps with keys of their own over one set of values)
+//   out_f32      the result is written as float32 whatever q's dtype (for a caller that still
+//                combines maps before anything is rounded)
 //
 // What it computes, per query token at absolute position p of request b and query head h
 // (kv head h / (H / KV)):   o = softmax_k( q . k_k * scale ) v_k   over keys k <= p
@@ -48,6 +52,7 @@ struct AttnParams {
     const int* bucket;   // [n_bucket]: row of rel for a distance (distances beyond the table take its last entry)
     const void* gate;    // [T, n_heads] (gate_mode 1) or [T, n_heads * v_head_dim] (gate_mode 2), in q's dtype
     int gate_mode, n_bucket, keep_first;
+    int n_v_heads, out_f32;
     int table_stride;
     int n_heads, n_kv_heads, head_dim, v_head_dim, page_size;
     int group, gchunk, n_gchunks, tokens_per_tile;
@@ -128,6 +133,7 @@ __global__ void __launch_bounds__(NT) paged_attention_kernel(const AttnParams p)
     const bool vec_ok = hd % VEC == 0 && dv % VEC == 0;      // every stored vector starts on 16 bytes
     const int k_vecs = hd / VEC, v_vecs = dv / VEC;
     const int* table = p.block_table + (size_t)b * p.table_stride;
+    const int vh = kvh % p.n_v_heads;        // the value head that goes with this key head
 
     for (int k0 = k_lo; k0 < k_hi; k0 += TK) {
         __syncthreads();  // the previous tile's Ks / Vs / Ss are no longer read (and Qs is written)
@@ -141,8 +147,9 @@ __global__ void __launch_bounds__(NT) paged_attention_kernel(const AttnParams p)
                 if (u < k_hi && tl_check_page(table[kpos / p.page_size])) {     // (debug builds: a bad page reads as zeros)
                     const int page = table[kpos / p.page_size];
                     const size_t at = ((size_t)page * p.n_kv_heads + kvh) * p.page_size + kpos % p.page_size;
+                    const size_t vat = ((size_t)page * p.n_v_heads + vh) * p.page_size + kpos % p.page_size;
                     Vec16<T> x;
-                    x.load(is_k ? k_pages + at * hd + v * VEC : v_pages + at * dv + (v - k_vecs) * VEC);
+                    x.load(is_k ? k_pages + at * hd + v * VEC : v_pages + vat * dv + (v - k_vecs) * VEC);
 #pragma unroll
                     for (int e = 0; e < VEC; ++e) dst[e] = x.get(e);
                 } else {
@@ -160,7 +167,8 @@ __global__ void __launch_bounds__(NT) paged_attention_kernel(const AttnParams p)
                 if (u < k_hi && tl_check_page(table[kpos / p.page_size])) {
                     const int page = table[kpos / p.page_size];
                     const size_t at = ((size_t)page * p.n_kv_heads + kvh) * p.page_size + kpos % p.page_size;
-                    x = to_float(is_k ? k_pages[at * hd + d] : v_pages[at * dv + (d - hd)]);
+                    const size_t vat = ((size_t)page * p.n_v_heads + vh) * p.page_size + kpos % p.page_size;
+                    x = to_float(is_k ? k_pages[at * hd + d] : v_pages[vat * dv + (d - hd)]);
                 }
                 if (is_k) Ks[j * qpitch + d] = x;
                 else Vs[j * dv + (d - hd)] = x;
@@ -227,13 +235,17 @@ __global__ void __launch_bounds__(NT) paged_attention_kernel(const AttnParams p)
     const size_t row = (size_t)tok * p.n_heads + head;
     if (p.n_splits == 1) {
         T* o = reinterpret_cast<T*>(p.out) + row * dv;
+        float* o32 = reinterpret_cast<float*>(p.out) + row * dv;
         float inv = l > 0.f ? 1.f / l : 0.f;
         const T* gate = reinterpret_cast<const T*>(p.gate);
         if (p.gate_mode == 1) inv *= to_float(gate[row]);
 #pragma unroll
         for (int jd = 0; jd < HD_MAX / 8; ++jd)
-            if (c + jd * 8 < dv)
-                o[c + jd * 8] = from_float<T>(acc[jd] * inv * (p.gate_mode == 2 ? to_float(gate[row * dv + c + jd * 8]) : 1.f));
+            if (c + jd * 8 < dv) {
+                const float v = acc[jd] * inv * (p.gate_mode == 2 ? to_float(gate[row * dv + c + jd * 8]) : 1.f);
+                if (p.out_f32) o32[c + jd * 8] = v;
+                else o[c + jd * 8] = from_float<T>(v);
+            }
     } else {
         float* o = p.part_o + (row * p.n_splits + split) * dv;
 #pragma unroll
@@ -251,7 +263,7 @@ __global__ void __launch_bounds__(NT) paged_attention_kernel(const AttnParams p)
 template <typename T>
 __global__ void attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                        T* __restrict__ out, int n_splits, int head_dim,
-                                       const T* __restrict__ gate, int gate_mode) {
+                                       const T* __restrict__ gate, int gate_mode, int out_f32) {
     const size_t row = blockIdx.x;
     const float* ml = part_ml + row * n_splits * 2;
     float M = -INFINITY;
@@ -268,7 +280,8 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_o, const f
         float o = den > 0.f ? num / den : 0.f;
         if (gate_mode == 1) o *= to_float(gate[row]);
         else if (gate_mode == 2) o *= to_float(gate[row * head_dim + d]);
-        out[row * head_dim + d] = from_float<T>(o);
+        if (out_f32) reinterpret_cast<float*>(out)[row * head_dim + d] = o;
+        else out[row * head_dim + d] = from_float<T>(o);
     }
 }
 
@@ -335,6 +348,8 @@ struct TlAttentionOptions {
     int n_bucket;
     const void* gate;       // in q's dtype
     int gate_mode;          // 0: none, 1: [tokens, n_heads], 2: [tokens, n_heads * v_head_dim]
+    int n_v_heads;          // 0: as n_kv_heads; else it divides n_kv_heads, and v_pages has so many heads
+    int out_f32;            // 1: out is float32 whatever q's dtype
 };
 
 // How many key splits the general kernel would use for this batch, and how many float32 words of
@@ -380,6 +395,8 @@ extern "C" int tl_paged_attention_ex(const void* q, const void* k_pages, const v
     if (o.keep_first < 0 || (o.keep_first > 0 && window == 0)) return TL_BAD_SIZE;
     if (o.rel != nullptr && (o.bucket == nullptr || o.n_bucket <= 0)) return TL_BAD_SIZE;
     if (o.gate_mode < 0 || o.gate_mode > 2 || (o.gate_mode != 0 && o.gate == nullptr)) return TL_BAD_SIZE;
+    if (o.n_v_heads <= 0) o.n_v_heads = n_kv_heads;
+    if (n_kv_heads % o.n_v_heads != 0 || (o.n_v_heads != n_kv_heads && v_pages == k_pages)) return TL_BAD_SIZE;
     if (!aligned16(q) || !aligned16(k_pages) || !aligned16(v_pages) || !aligned16(out)) return TL_BAD_ALIGN;
     const Plan pl = make_plan(n_seqs, n_heads, n_kv_heads, max_q_len, max_kv_len, allow_split, window, o.keep_first);
     if (pl.n_splits > 1 && workspace == nullptr) return TL_BAD_SIZE;
@@ -398,6 +415,7 @@ extern "C" int tl_paged_attention_ex(const void* q, const void* k_pages, const v
     p.keep_first = o.keep_first;
     p.rel = o.rel; p.bucket = o.bucket; p.n_bucket = o.n_bucket;
     p.gate = o.gate; p.gate_mode = o.gate_mode;
+    p.n_v_heads = o.n_v_heads; p.out_f32 = o.out_f32;
     p.n_splits = pl.n_splits;
     p.scale = scale;
     p.part_o = workspace;
@@ -415,10 +433,10 @@ extern "C" int tl_paged_attention_ex(const void* q, const void* k_pages, const v
         const unsigned rows = (unsigned)n_tokens * n_heads;
         if (dtype == TL_F32)
             attention_merge_kernel<float><<<rows, threads, 0, s>>>(p.part_o, p.part_ml, (float*)out, pl.n_splits, o.v_head_dim,
-                                                                    (const float*)o.gate, o.gate_mode);
+                                                                    (const float*)o.gate, o.gate_mode, o.out_f32);
         else
             attention_merge_kernel<__nv_bfloat16><<<rows, threads, 0, s>>>(p.part_o, p.part_ml, (__nv_bfloat16*)out, pl.n_splits,
-                                                                            o.v_head_dim, (const __nv_bfloat16*)o.gate, o.gate_mode);
+                                                                            o.v_head_dim, (const __nv_bfloat16*)o.gate, o.gate_mode, o.out_f32);
         TL_LAUNCH_CHECK();
     }
     return TL_OK;

@@ -65,6 +65,8 @@ struct MmaParams {
     const __nv_bfloat16* gate;
     int gate_mode;              // 0: none, 1: [T, n_heads], 2: [T, n_heads * dv]
     int bias_cols;              // row split: the bias of so many distances (from 0) is tabulated in shared memory per head of the tile
+    int n_v_heads;              // value heads of v_pages; key head j goes with value head j % n_v_heads
+    int out_f32;                // 1: out holds float32
 };
 
 __device__ __forceinline__ unsigned smem_addr(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -195,9 +197,10 @@ __global__ void __launch_bounds__(NT, KEY_SPLIT ? 4 : 2) attention_mma_kernel(co
     constexpr int LD_STEP = NT / CHUNKS;          // keys between two chunks of one thread
     constexpr int LD_ITERS = BN / LD_STEP;
     const size_t page_stride_k = (size_t)p.n_kv_heads * p.page_size * hd;
-    const size_t page_stride_v = (size_t)p.n_kv_heads * p.page_size * dv;
+    const int n_vh = EXT ? p.n_v_heads : p.n_kv_heads;
+    const size_t page_stride_v = (size_t)n_vh * p.page_size * dv;
     const size_t head_off_k = (size_t)kvh * p.page_size * hd + ld_part;
-    const size_t head_off_v = (size_t)kvh * p.page_size * dv + ld_part;
+    const size_t head_off_v = (size_t)(kvh % n_vh) * p.page_size * dv + ld_part;
     const bool k_real = ld_part < hd, v_real = ld_part < dv && !(EXT && p.shared_kv);
     auto load_tile = [&](int stage, int k0, int k_end) {
         __nv_bfloat16* kd = Ks + stage * BN * PITCH + ld_part;
@@ -436,7 +439,8 @@ __global__ void __launch_bounds__(NT, KEY_SPLIT ? 4 : 2) attention_mma_kernel(co
                     a *= gv.x;
                     c *= gv.y;
                 }
-                *reinterpret_cast<unsigned*>(dst + nt * 8 + 2 * t) = pack_bf16(a, c);
+                if (EXT && p.out_f32) *reinterpret_cast<float2*>(reinterpret_cast<float*>(p.out) + row * dv + nt * 8 + 2 * t) = make_float2(a, c);
+                else *reinterpret_cast<unsigned*>(dst + nt * 8 + 2 * t) = pack_bf16(a, c);
             }
         }
         return;
@@ -484,7 +488,8 @@ __global__ void __launch_bounds__(NT, KEY_SPLIT ? 4 : 2) attention_mma_kernel(co
             float v = den > 0.f ? num / den : 0.f;
             if (EXT && p.gate_mode == 1) v *= __bfloat162float(p.gate[row]);
             else if (EXT && p.gate_mode == 2) v *= __bfloat162float(p.gate[row * dv + d]);
-            p.out[row * dv + d] = __float2bfloat16_rn(v);
+            if (EXT && p.out_f32) reinterpret_cast<float*>(p.out)[row * dv + d] = v;
+            else p.out[row * dv + d] = __float2bfloat16_rn(v);
         } else {
             p.part_o[(row * p.n_splits + split) * dv + d] = num;
             if (d == 0) {
@@ -501,7 +506,7 @@ __global__ void __launch_bounds__(NT, KEY_SPLIT ? 4 : 2) attention_mma_kernel(co
 constexpr int MERGE_MAX_SPLITS = 256;
 __global__ void merge_partials_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                       __nv_bfloat16* __restrict__ out, int n_splits, int head_dim,
-                                      const __nv_bfloat16* __restrict__ gate = nullptr, int gate_mode = 0) {
+                                      const __nv_bfloat16* __restrict__ gate = nullptr, int gate_mode = 0, int out_f32 = 0) {
     __shared__ float wgt[MERGE_MAX_SPLITS];
     __shared__ float red[2];
     const size_t row = blockIdx.x;
@@ -529,7 +534,8 @@ __global__ void merge_partials_kernel(const float* __restrict__ part_o, const fl
         float v = num * inv;
         if (gate_mode == 1) v *= __bfloat162float(gate[row]);
         else if (gate_mode == 2) v *= __bfloat162float(gate[row * head_dim + d]);
-        out[row * head_dim + d] = __float2bfloat16_rn(v);
+        if (out_f32) reinterpret_cast<float*>(out)[row * head_dim + d] = v;
+        else out[row * head_dim + d] = __float2bfloat16_rn(v);
     }
 }
 
@@ -654,7 +660,7 @@ extern "C" int tl_paged_attention_mma(const void* q, const void* k_pages, const 
     p.scale_log2 = scale * LOG2E;
     p.part_o = workspace;
     p.part_ml = workspace ? workspace + (size_t)n_tokens * n_heads * pl.n_splits * head_dim : nullptr;
-    p.hd = p.dv = head_dim; p.shared_kv = 0; p.keep_first = 0; p.rel = nullptr; p.bucket = nullptr; p.n_bucket = 0;
+    p.hd = p.dv = head_dim; p.shared_kv = 0; p.keep_first = 0; p.rel = nullptr; p.bucket = nullptr; p.n_bucket = 0; p.n_v_heads = n_kv_heads; p.out_f32 = 0;
     p.gate = nullptr; p.gate_mode = 0; p.bias_cols = 0;
 
     cudaStream_t s = (cudaStream_t)stream;
@@ -685,6 +691,8 @@ struct TlAttentionOptions {
     int n_bucket;
     const void* gate;       // bfloat16
     int gate_mode;          // 0: none, 1: [tokens, n_heads], 2: [tokens, n_heads * v_head_dim]
+    int n_v_heads;          // 0: as n_kv_heads; else it divides n_kv_heads, and v_pages has so many heads
+    int out_f32;            // 1: out is float32
 };
 
 // 1 if the extended form takes keys of head_dim and values of v_head_dim elements, else 0.
@@ -720,6 +728,8 @@ extern "C" int tl_paged_attention_mma_ex(const void* q, const void* k_pages, con
     if (o.rel != nullptr && (o.bucket == nullptr || o.n_bucket <= 0)) return TL_BAD_SIZE;
     if (o.gate_mode < 0 || o.gate_mode > 2 || (o.gate_mode != 0 && o.gate == nullptr)) return TL_BAD_SIZE;
     if (v_pages == k_pages && dv != head_dim) return TL_BAD_SIZE;
+    const int n_v_heads = o.n_v_heads > 0 ? o.n_v_heads : n_kv_heads;
+    if (n_kv_heads % n_v_heads != 0 || (n_v_heads != n_kv_heads && v_pages == k_pages)) return TL_BAD_SIZE;
     if (!aligned16(q) || !aligned16(k_pages) || !aligned16(v_pages) || !aligned16(out)) return TL_BAD_ALIGN;
     const Plan pl = make_plan(n_seqs, n_heads, n_kv_heads, max_q_len, max_kv_len, allow_split, window, o.keep_first);
     if (pl.n_splits > 1 && workspace == nullptr) return TL_BAD_SIZE;
@@ -742,6 +752,7 @@ extern "C" int tl_paged_attention_mma_ex(const void* q, const void* k_pages, con
     p.hd = head_dim; p.dv = dv; p.shared_kv = v_pages == k_pages ? 1 : 0;
     p.keep_first = o.keep_first; p.rel = o.rel; p.bucket = o.bucket; p.n_bucket = o.n_bucket;
     p.gate = (const __nv_bfloat16*)o.gate; p.gate_mode = o.gate_mode;
+    p.n_v_heads = n_v_heads; p.out_f32 = o.out_f32 ? 1 : 0;
     // distances a row-split CTA meets inside its window (all of them when there is no window), as far as
     // 20 KB of shared memory hold them for the heads of a tile
     p.bias_cols = 0;
@@ -764,7 +775,7 @@ extern "C" int tl_paged_attention_mma_ex(const void* q, const void* k_pages, con
     if (rc != TL_OK) return rc;
     if (pl.n_splits > 1) {
         merge_partials_kernel<<<dim3((unsigned)n_tokens * (unsigned)n_heads), dim3(dv >= 128 ? 128u : 64u), 0, s>>>(
-            p.part_o, p.part_ml, p.out, pl.n_splits, dv, p.gate, p.gate_mode);
+            p.part_o, p.part_ml, p.out, pl.n_splits, dv, p.gate, p.gate_mode, p.out_f32);
         TL_LAUNCH_CHECK();
     }
     return TL_OK;

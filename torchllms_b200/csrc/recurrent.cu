@@ -1,0 +1,150 @@
+// Recurrences with a state of fixed size per request.
+//
+// mingru_scan: a gated recurrence whose gates read the current token only.  A token's row of the
+// stacked projection is [z | u | g], W columns each (a bias is added first):
+//     a = sigmoid(z);   c = u + 1/2 where u >= 0, sigmoid(u) elsewhere;
+//     S <- (1 - a) S + a c      (element by element; S is the request's state row, float32)
+//     out = S * g * sigmoid(g)
+// Everything is float32 arithmetic; the projection may arrive as bfloat16 or as float32 partial
+// sums of a split-K product, the result leaves in the activation dtype.
+//
+// A request's portion is a linear recurrence S_t = p_t S_(t-1) + r_t, so it can be cut into chunks:
+// every chunk first reduces to the pair (P, R) with S_end = P S_start + R (kernel 1, all chunks side
+// by side), then each chunk finds its own S_start by walking the pairs of the chunks before it and
+// runs its tokens again, writing the outputs (kernel 2).  Portions no longer than one chunk (decode
+// steps among them) run as kernel 2 alone.  A thread owns one column of one chunk, so reads are
+// side by side along the row.
+#include "common.cuh"
+
+namespace {
+
+constexpr int CHUNK = 64;     // tokens a thread walks in one go
+constexpr int NT = 128;
+
+struct ScanParams {
+    const void* proj;        // [splits][T][3 W]
+    int splits;
+    long long plane;
+    const float* bias;       // [3 W] or null
+    float* state;            // [slots][W]
+    const int* q_start;      // [B + 1]
+    const int* state_slot;   // [B]
+    const int* fresh;        // [B]: 1 where the request starts here (its state counts as zero)
+    void* out;               // [T][W]
+    float* pairs;            // [B][n_chunks][2][W]: P and R of every chunk
+    float* start;            // [B][W]: the state as the step found it
+    int W, n_chunks;
+};
+
+template <typename TI>
+__device__ __forceinline__ float column(const ScanParams& p, size_t at) {
+    const TI* src = reinterpret_cast<const TI*>(p.proj);
+    float x = 0.f;
+    for (int s = 0; s < p.splits; ++s) x += to_float(src[(size_t)s * p.plane + at]);
+    return x;
+}
+
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + expf(-x)); }
+
+// (keep, add) of one token for column c: S <- keep * S + add
+template <typename TI>
+__device__ __forceinline__ void token_terms(const ScanParams& p, int t, int c, float bz, float bu, float& keep, float& add) {
+    const size_t row = (size_t)t * 3 * p.W;
+    const float a = sigmoidf_(column<TI>(p, row + c) + bz);
+    const float u = column<TI>(p, row + p.W + c) + bu;
+    const float cand = u >= 0.f ? u + 0.5f : sigmoidf_(u);
+    keep = 1.f - a;
+    add = a * cand;
+}
+
+template <typename TI>
+__global__ void __launch_bounds__(NT) mingru_pairs_kernel(const ScanParams p) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const int c = blockIdx.x * NT + threadIdx.x;
+    const int chunk = blockIdx.y, b = blockIdx.z;
+    if (c >= p.W) return;
+    const int t0 = p.q_start[b] + chunk * CHUNK, t_end = min(p.q_start[b + 1], t0 + CHUNK);
+    if (chunk == 0) p.start[(size_t)b * p.W + c] = p.fresh[b] ? 0.f : p.state[(size_t)p.state_slot[b] * p.W + c];
+    if (t0 >= t_end) return;
+    const float bz = p.bias ? p.bias[c] : 0.f, bu = p.bias ? p.bias[p.W + c] : 0.f;
+    float P = 1.f, R = 0.f;
+    for (int t = t0; t < t_end; ++t) {
+        float keep, add;
+        token_terms<TI>(p, t, c, bz, bu, keep, add);
+        P *= keep;
+        R = fmaf(keep, R, add);
+    }
+    float* pr = p.pairs + ((size_t)b * p.n_chunks + chunk) * 2 * p.W;
+    pr[c] = P;
+    pr[p.W + c] = R;
+}
+
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(NT) mingru_scan_kernel(const ScanParams p) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const int c = blockIdx.x * NT + threadIdx.x;
+    const int chunk = blockIdx.y, b = blockIdx.z;
+    if (c >= p.W) return;
+    const int t0 = p.q_start[b] + chunk * CHUNK, t_last = p.q_start[b + 1], t_end = min(t_last, t0 + CHUNK);
+    if (t0 >= t_end) return;
+    float S;
+    if (p.n_chunks == 1) {
+        S = p.fresh[b] ? 0.f : p.state[(size_t)p.state_slot[b] * p.W + c];
+    } else {
+        S = p.start[(size_t)b * p.W + c];
+        const float* pr = p.pairs + (size_t)b * p.n_chunks * 2 * p.W;
+        for (int j = 0; j < chunk; ++j) S = fmaf(pr[(size_t)j * 2 * p.W + c], S, pr[(size_t)j * 2 * p.W + p.W + c]);
+    }
+    const float bz = p.bias ? p.bias[c] : 0.f, bu = p.bias ? p.bias[p.W + c] : 0.f, bg = p.bias ? p.bias[2 * p.W + c] : 0.f;
+    TO* out = reinterpret_cast<TO*>(p.out);
+    for (int t = t0; t < t_end; ++t) {
+        float keep, add;
+        token_terms<TI>(p, t, c, bz, bu, keep, add);
+        S = fmaf(keep, S, add);
+        const float g = column<TI>(p, (size_t)t * 3 * p.W + 2 * p.W + c) + bg;
+        out[(size_t)t * p.W + c] = from_float<TO>(S * g * sigmoidf_(g));
+    }
+    if (t_end == t_last) p.state[(size_t)p.state_slot[b] * p.W + c] = S;     // the portion's last chunk leaves the state
+}
+
+}  // namespace
+
+// float32 words of scratch that a call with these sizes needs (0: none)
+extern "C" long long tl_mingru_scan_scratch(int n_seqs, int width, int max_q_len) {
+    const long long n_chunks = (max_q_len + CHUNK - 1) / CHUNK;
+    return n_chunks <= 1 ? 0 : (long long)n_seqs * width * (2 * n_chunks + 1);
+}
+
+// proj: [splits][n_tokens][3 * width] of in_dtype; bias: float32 [3 * width] or null; state: float32
+// [slots][width]; out: [n_tokens][width] of out_dtype; scratch: as tl_mingru_scan_scratch says.
+extern "C" int tl_mingru_scan(const void* proj, int in_dtype, int splits, long long plane, const float* bias, float* state,
+                              const int* q_start, const int* state_slot, const int* fresh, void* out, int out_dtype,
+                              int n_tokens, int n_seqs, int width, int max_q_len, float* scratch, void* stream) {
+    if (n_tokens <= 0 || n_seqs <= 0) return TL_OK;
+    if (width <= 0 || max_q_len <= 0 || splits < 1 || n_seqs > 65535) return TL_BAD_SIZE;
+    ScanParams p;
+    p.proj = proj; p.splits = splits; p.plane = plane; p.bias = bias; p.state = state;
+    p.q_start = q_start; p.state_slot = state_slot; p.fresh = fresh; p.out = out;
+    p.W = width;
+    p.n_chunks = (max_q_len + CHUNK - 1) / CHUNK;
+    if (p.n_chunks > 65535) return TL_BAD_SIZE;
+    if (p.n_chunks > 1 && scratch == nullptr) return TL_BAD_SIZE;
+    p.start = scratch;
+    p.pairs = scratch ? scratch + (size_t)n_seqs * width : nullptr;
+    cudaStream_t s = (cudaStream_t)stream;
+    const dim3 grid((width + NT - 1) / NT, p.n_chunks, n_seqs), block(NT);
+    cudaError_t e = cudaSuccess;
+#define TL_SCAN(TI, TO)                                                                          \
+    do {                                                                                         \
+        if (p.n_chunks > 1) e = tl_launch(mingru_pairs_kernel<TI>, grid, block, 0, s, p);        \
+        if (e == cudaSuccess) e = tl_launch(mingru_scan_kernel<TI, TO>, grid, block, 0, s, p);   \
+    } while (0)
+    if (in_dtype == TL_F32 && out_dtype == TL_F32) TL_SCAN(float, float);
+    else if (in_dtype == TL_F32 && out_dtype == TL_BF16) TL_SCAN(float, __nv_bfloat16);
+    else if (in_dtype == TL_BF16 && out_dtype == TL_BF16) TL_SCAN(__nv_bfloat16, __nv_bfloat16);
+    else return TL_BAD_DTYPE;
+#undef TL_SCAN
+    return (int)e;
+}

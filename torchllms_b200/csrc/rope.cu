@@ -228,3 +228,100 @@ extern "C" int tl_rope_kv_write(const void* qkv, int in_dtype, int splits, const
 #undef TL_ROPE_LAUNCH
     return TL_BAD_DTYPE;
 }
+
+// ---------------------------------------------------------------------------------------------
+// The general form: a row [q heads | k heads | v heads | extra] in which keys and values have head
+// counts and sizes of their own, only the first rot_dims coordinates of a q or k head are rotated
+// (the table has rot_dims / 2 (cos, sin) pairs a position), and the extra columns leave as their
+// sigmoids (gates that ride in the same projection).  k_pages: [pages, n_k_heads, page_size,
+// head_dim]; v_pages: [pages, n_v_heads, page_size, v_head_dim].  One CTA per token.
+template <typename TI, typename T>
+__global__ void rope_store_kernel(const TI* __restrict__ proj, int splits, long long plane,
+                                  const int* __restrict__ positions, const float* __restrict__ table,
+                                  const int* __restrict__ slot_mapping, T* __restrict__ q_out, T* __restrict__ extra_out,
+                                  T* __restrict__ k_pages, T* __restrict__ v_pages, int n_q_heads, int n_k_heads,
+                                  int n_v_heads, int head_dim, int v_head_dim, int rot_dims, int n_extra, int page_size,
+                                  int table_rows, int interleaved) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const int t = blockIdx.x;
+    const int half = rot_dims >> 1;
+    int pos = positions[t];
+    (void)TL_CHECK(pos >= 0 && pos < table_rows, TL_DBG_POSITION);
+    pos = pos < 0 ? 0 : (pos >= table_rows ? table_rows - 1 : pos);
+    const float* cs = table + (size_t)pos * rot_dims;      // [half][2]
+    const int qk_heads = n_q_heads + n_k_heads;
+    const int n_qk = qk_heads * head_dim, n_v = n_v_heads * v_head_dim;
+    const int width = n_qk + n_v + n_extra;
+    const TI* src = proj + (size_t)t * width;
+    int page = 0, slot = 0;
+    bool write = k_pages != nullptr && n_k_heads > 0;
+    if (write) {
+        const int sm = slot_mapping[t];
+        page = sm / page_size;
+        slot = sm - page * page_size;
+        if (!(TL_CHECK(sm >= 0, TL_DBG_SLOT) && tl_check_page(page))) write = false;
+    }
+    auto value = [&](int c) {
+        float x = 0.f;
+        for (int sp = 0; sp < splits; ++sp) x += to_float(src[(size_t)sp * plane + c]);
+        return x;
+    };
+    auto put_qk = [&](int head, int d, float x) {
+        if (head < n_q_heads) q_out[((size_t)t * n_q_heads + head) * head_dim + d] = from_float<T>(x);
+        else if (write)
+            k_pages[(((size_t)page * n_k_heads + (head - n_q_heads)) * page_size + slot) * head_dim + d] = from_float<T>(x);
+    };
+    // a head's work items: `half` rotated pairs, then the coordinates that pass
+    const int per_head = head_dim - half;
+    for (int w = threadIdx.x; w < qk_heads * per_head; w += blockDim.x) {
+        const int head = w / per_head, i = w - head * per_head;
+        if (i < half) {
+            const int l0 = interleaved ? 2 * i : i, l1 = interleaved ? 2 * i + 1 : i + half;
+            const float x0 = value(head * head_dim + l0), x1 = value(head * head_dim + l1);
+            const float c = cs[2 * i], s = cs[2 * i + 1];
+            put_qk(head, l0, x0 * c - x1 * s);
+            put_qk(head, l1, x1 * c + x0 * s);
+        } else {
+            const int d = i + half;
+            put_qk(head, d, value(head * head_dim + d));
+        }
+    }
+    if (write && v_pages != nullptr) {
+        for (int c = threadIdx.x; c < n_v; c += blockDim.x) {
+            const int head = c / v_head_dim, d = c - head * v_head_dim;
+            v_pages[(((size_t)page * n_v_heads + head) * page_size + slot) * v_head_dim + d] = from_float<T>(value(n_qk + c));
+        }
+    }
+    for (int c = threadIdx.x; c < n_extra; c += blockDim.x)
+        extra_out[(size_t)t * n_extra + c] = from_float<T>(1.f / (1.f + expf(-value(n_qk + n_v + c))));
+}
+
+// proj: [splits, n_tokens, width] of in_dtype, width = (n_q_heads + n_k_heads) * head_dim + n_v_heads * v_head_dim
+// + n_extra; n_k_heads = n_v_heads = 0 for a run that reads another run's cache (pages may then be null);
+// table: float32 [table_rows, rot_dims / 2, 2]; q_out [n_tokens, n_q_heads, head_dim], extra_out [n_tokens, n_extra]
+// and the pages in dtype.
+extern "C" int tl_rope_store(const void* proj, int in_dtype, int splits, const int* positions, const float* table,
+                             const int* slot_mapping, void* q_out, void* extra_out, void* k_pages, void* v_pages, int dtype,
+                             int n_tokens, int n_q_heads, int n_k_heads, int n_v_heads, int head_dim, int v_head_dim,
+                             int rot_dims, int n_extra, int page_size, int table_rows, int interleaved, void* stream) {
+    if (n_tokens <= 0) return TL_OK;
+    if (head_dim <= 0 || n_q_heads <= 0 || n_k_heads < 0 || n_v_heads < 0 || v_head_dim < 0 || n_extra < 0 || splits < 1 ||
+        rot_dims < 0 || (rot_dims & 1) || rot_dims > head_dim || page_size <= 0 || table_rows <= 0)
+        return TL_BAD_SIZE;
+    if (n_k_heads > 0 && k_pages != nullptr && (slot_mapping == nullptr || (n_v_heads > 0 && v_pages == nullptr))) return TL_BAD_SIZE;
+    if (n_extra > 0 && extra_out == nullptr) return TL_BAD_SIZE;
+    const long long width = (long long)(n_q_heads + n_k_heads) * head_dim + (long long)n_v_heads * v_head_dim + n_extra;
+    const long long plane = (long long)n_tokens * width;
+    const int threads = width >= 2048 ? 256 : 128;
+    cudaStream_t s = (cudaStream_t)stream;
+#define TL_ROPE_STORE(TI, T)                                                                                          \
+    tl_launch(rope_store_kernel<TI, T>, dim3(n_tokens), dim3(threads), 0, s, (const TI*)proj, splits, plane, positions, \
+              table, slot_mapping, (T*)q_out, (T*)extra_out, (T*)k_pages, (T*)v_pages, n_q_heads, n_k_heads, n_v_heads, \
+              head_dim, v_head_dim, rot_dims, n_extra, page_size, table_rows, interleaved)
+    if (in_dtype == TL_F32 && dtype == TL_F32) return (int)TL_ROPE_STORE(float, float);
+    if (in_dtype == TL_BF16 && dtype == TL_BF16) return (int)TL_ROPE_STORE(__nv_bfloat16, __nv_bfloat16);
+    if (in_dtype == TL_F32 && dtype == TL_BF16) return (int)TL_ROPE_STORE(float, __nv_bfloat16);
+#undef TL_ROPE_STORE
+    return TL_BAD_DTYPE;
+}

@@ -502,3 +502,241 @@ extern "C" int tl_project_store(const void* proj, int in_dtype, int splits, long
 #undef TL_PROJECT_LAUNCH
     return (int)e;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Layers with a norm in front of each sublayer and another on its output, gated and plain
+// activations by name, an average over the results of all layers so far, and the combination of
+// two attention maps:
+//
+// norm_add_norm:   d = sum of delta's planes;  h[t] += d / sqrt(mean(d^2) + eps) * w   (float32), and
+//                  out[t] = h[t] / sqrt(mean(h[t]^2) + eps2) * w2: the output norm of one sublayer, the
+//                  residual sum and the input norm of the next sublayer in one pass over the row
+// depth_mix:       out = sum_j c[j] * level_j over the first n levels of [levels][tokens][dim]
+// gated_act:       act(gate) * up for a row [gate | up];  activation: act(x)      (float32 arithmetic)
+// differential_combine:  per (token, head): o = a1 - lambda a2 over the head's values, then
+//                  o / sqrt(mean(o^2) + eps) * out_scale * gate[token, head]
+namespace {
+
+enum : int { ACT_SILU = 0, ACT_GELU_TANH = 1, ACT_RELU2 = 2 };
+
+__device__ __forceinline__ float act_apply(float x, int act) {
+    if (act == ACT_SILU) return x / (1.f + expf(-x));
+    if (act == ACT_GELU_TANH) return 0.5f * x * (1.f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+    const float r = fmaxf(x, 0.f);
+    return r * r;
+}
+
+// One CTA per row; the row is kept in shared memory between the passes.  VEC: four columns per thread and turn.
+template <typename TD, typename TO, bool VEC>
+__global__ void norm_add_norm_kernel(float* __restrict__ h, const TD* __restrict__ delta, int splits, long long plane,
+                                     const float* __restrict__ weight, const float* __restrict__ weight2,
+                                     TO* __restrict__ out, int dim, float eps, float eps2) {
+    extern __shared__ __align__(16) float row_buf[];
+    __shared__ float part[33];
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const size_t base = (size_t)blockIdx.x * dim;
+    float ssq = 0.f;
+    if (VEC) {
+        for (int d = threadIdx.x * 4; d < dim; d += blockDim.x * 4) {
+            const float4 v = sum_planes4(delta + base + d, splits, plane);
+            st4(row_buf + d, v);
+            ssq += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+    } else {
+        for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+            float v = 0.f;
+            for (int s = 0; s < splits; ++s) v += to_float(delta[(size_t)s * plane + base + d]);
+            row_buf[d] = v;
+            ssq = fmaf(v, v, ssq);
+        }
+    }
+    const float r = rsqrtf(block_sum(ssq, part) / (float)dim + eps);
+    float ssq2 = 0.f;
+    if (VEC) {
+        for (int d = threadIdx.x * 4; d < dim; d += blockDim.x * 4) {
+            const float4 x = ld4(row_buf + d), w = ld4(weight + d);
+            float4 v = ld4(h + base + d);
+            v.x += x.x * r * w.x; v.y += x.y * r * w.y; v.z += x.z * r * w.z; v.w += x.w * r * w.w;
+            st4(h + base + d, v);
+            st4(row_buf + d, v);
+            ssq2 += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+    } else {
+        for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+            const float v = h[base + d] + row_buf[d] * r * weight[d];
+            h[base + d] = v;
+            row_buf[d] = v;
+            ssq2 = fmaf(v, v, ssq2);
+        }
+    }
+    const float r2 = rsqrtf(block_sum(ssq2, part) / (float)dim + eps2);
+    if (VEC) {
+        for (int d = threadIdx.x * 4; d < dim; d += blockDim.x * 4) {
+            const float4 x = ld4(row_buf + d), w = ld4(weight2 + d);
+            st4(out + base + d, make_float4(x.x * r2 * w.x, x.y * r2 * w.y, x.z * r2 * w.z, x.w * r2 * w.w));
+        }
+    } else {
+        for (int d = threadIdx.x; d < dim; d += blockDim.x) out[base + d] = from_float<TO>(row_buf[d] * r2 * weight2[d]);
+    }
+}
+
+template <bool VEC>
+__global__ void depth_mix_kernel(const float* __restrict__ levels, long long level_stride, const float* __restrict__ coef,
+                                 int n, float* __restrict__ out, long long count) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const long long step = (long long)gridDim.x * blockDim.x;
+    if (VEC) {
+        for (long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < count; i += step * 4) {
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int j = 0; j < n; ++j) {
+                const float c = __ldg(coef + j);
+                const float4 v = ld4(levels + j * level_stride + i);
+                acc.x = fmaf(c, v.x, acc.x); acc.y = fmaf(c, v.y, acc.y); acc.z = fmaf(c, v.z, acc.z); acc.w = fmaf(c, v.w, acc.w);
+            }
+            st4(out + i, acc);
+        }
+    } else {
+        for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += step) {
+            float acc = 0.f;
+            for (int j = 0; j < n; ++j) acc = fmaf(__ldg(coef + j), levels[j * level_stride + i], acc);
+            out[i] = acc;
+        }
+    }
+}
+
+// in: [splits][n_tokens][(gated ? 2 : 1) * hidden]; out: [n_tokens][hidden]
+template <typename TI, typename TO>
+__global__ void act_kernel(const TI* __restrict__ in, int splits, long long plane, TO* __restrict__ out,
+                           long long n_tokens, int hidden, int act, int gated) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const long long total = n_tokens * hidden;
+    const int width = gated ? 2 * hidden : hidden;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long t = i / hidden;
+        const int f = (int)(i - t * hidden);
+        const size_t at = (size_t)t * width + f;
+        float g = 0.f, u = 0.f;
+        for (int s = 0; s < splits; ++s) {
+            g += to_float(in[(size_t)s * plane + at]);
+            if (gated) u += to_float(in[(size_t)s * plane + at + hidden]);
+        }
+        const float a = act_apply(g, act);
+        out[i] = from_float<TO>(gated ? a * u : a);
+    }
+}
+
+// maps: float32 [T][2 H][dv], all first maps before all second maps; a warp per (token, head)
+template <typename TO>
+__global__ void differential_combine_kernel(const float* __restrict__ maps, const TO* __restrict__ gate,
+                                            TO* __restrict__ out, long long n_rows, int n_heads, int dv, float lam,
+                                            float eps, float out_scale) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const int lane = threadIdx.x & 31;
+    const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);   // token * H + head
+    if (row >= n_rows) return;
+    const long long t = row / n_heads;
+    const int hd = (int)(row - t * n_heads);
+    const float* a1 = maps + ((size_t)t * 2 * n_heads + hd) * dv;
+    const float* a2 = a1 + (size_t)n_heads * dv;
+    float ssq = 0.f;
+    for (int d = lane; d < dv; d += 32) {
+        const float o = a1[d] - lam * a2[d];
+        ssq = fmaf(o, o, ssq);
+    }
+    ssq = warp_sum(ssq);
+    float f = rsqrtf(ssq / (float)dv + eps) * out_scale;
+    if (gate != nullptr) f *= to_float(gate[row]);
+    for (int d = lane; d < dv; d += 32) out[(size_t)row * dv + d] = from_float<TO>((a1[d] - lam * a2[d]) * f);
+}
+
+}  // namespace
+
+// As tl_norm_add, and out = norm of the new h under weight2 / eps2, in out_dtype.
+extern "C" int tl_norm_add_norm(float* h, const void* delta, int delta_dtype, int splits, long long plane,
+                                const float* weight, const float* weight2, void* out, int out_dtype, int n_rows, int dim,
+                                float eps, float eps2, void* stream) {
+    if (n_rows <= 0) return TL_OK;
+    if (dim <= 0 || splits < 1) return TL_BAD_SIZE;
+    const size_t smem = (size_t)dim * sizeof(float);
+    if (smem > 200 * 1024) return TL_TOO_LARGE;
+    cudaStream_t s = (cudaStream_t)stream;
+    const bool vec = dim % 4 == 0 && plane % 4 == 0 && aligned16(h) && aligned16(delta) && aligned16(weight) &&
+                     aligned16(weight2) && aligned16(out);
+    const dim3 grid(n_rows), block(vec ? vec_threads(dim, n_rows) : row_threads(dim));
+#define TL_NAN_LAUNCH(TD, TO, V)                                                                                     \
+    do {                                                                                                             \
+        static int raised = 0;                                                                                       \
+        if (smem > 48 * 1024 && (int)smem > raised) {                                                                \
+            cudaError_t e = cudaFuncSetAttribute(norm_add_norm_kernel<TD, TO, V>,                                    \
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);            \
+            if (e != cudaSuccess) return (int)e;                                                                     \
+            raised = (int)smem;                                                                                      \
+        }                                                                                                            \
+        return (int)tl_launch(norm_add_norm_kernel<TD, TO, V>, grid, block, smem, s, h, (const TD*)delta, splits,    \
+                              plane, weight, weight2, (TO*)out, dim, eps, eps2);                                     \
+    } while (0)
+#define TL_NAN_PICK(TD, TO) do { if (vec) TL_NAN_LAUNCH(TD, TO, true); else TL_NAN_LAUNCH(TD, TO, false); } while (0)
+    if (delta_dtype == TL_F32 && out_dtype == TL_F32) TL_NAN_PICK(float, float);
+    if (delta_dtype == TL_F32 && out_dtype == TL_BF16) TL_NAN_PICK(float, __nv_bfloat16);
+    if (delta_dtype == TL_BF16 && out_dtype == TL_BF16) TL_NAN_PICK(__nv_bfloat16, __nv_bfloat16);
+#undef TL_NAN_PICK
+#undef TL_NAN_LAUNCH
+    return TL_BAD_DTYPE;
+}
+
+// levels: float32 [>= n][count] with level_stride elements between levels; out: [count] (may be a later level)
+extern "C" int tl_depth_mix(const float* levels, long long level_stride, const float* coef, int n, float* out,
+                            long long count, void* stream) {
+    if (count <= 0) return TL_OK;
+    if (n < 1) return TL_BAD_SIZE;
+    const bool vec = count % 4 == 0 && level_stride % 4 == 0 && aligned16(levels) && aligned16(out);
+    long long blocks = ((vec ? count / 4 : count) + 255) / 256;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    if (vec) return (int)tl_launch(depth_mix_kernel<true>, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, levels,
+                                   level_stride, coef, n, out, count);
+    return (int)tl_launch(depth_mix_kernel<false>, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, levels,
+                          level_stride, coef, n, out, count);
+}
+
+// gated: in is [splits][n_tokens][2 * hidden] (gate columns first) and out = act(gate) * up; else in is
+// [splits][n_tokens][hidden] and out = act(in).  act: 0 silu, 1 gelu (tanh form), 2 squared relu.
+extern "C" int tl_act(const void* in, int in_dtype, int splits, long long plane, void* out, int out_dtype, int n_tokens,
+                      int hidden, int act, int gated, void* stream) {
+    if ((long long)n_tokens * hidden <= 0) return TL_OK;
+    if (splits < 1 || act < 0 || act > 2) return TL_BAD_SIZE;
+    cudaStream_t s = (cudaStream_t)stream;
+    long long blocks = ((long long)n_tokens * hidden + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    const dim3 grid((unsigned)blocks), block(256);
+    if (in_dtype == TL_F32 && out_dtype == TL_F32)
+        return (int)tl_launch(act_kernel<float, float>, grid, block, 0, s, (const float*)in, splits, plane, (float*)out,
+                              (long long)n_tokens, hidden, act, gated);
+    if (in_dtype == TL_F32 && out_dtype == TL_BF16)
+        return (int)tl_launch(act_kernel<float, __nv_bfloat16>, grid, block, 0, s, (const float*)in, splits, plane,
+                              (__nv_bfloat16*)out, (long long)n_tokens, hidden, act, gated);
+    if (in_dtype == TL_BF16 && out_dtype == TL_BF16)
+        return (int)tl_launch(act_kernel<__nv_bfloat16, __nv_bfloat16>, grid, block, 0, s, (const __nv_bfloat16*)in, splits,
+                              plane, (__nv_bfloat16*)out, (long long)n_tokens, hidden, act, gated);
+    return TL_BAD_DTYPE;
+}
+
+// maps: float32 [n_tokens][2 * n_heads][dv]; gate: [n_tokens][n_heads] in out_dtype or null; out: [n_tokens][n_heads * dv]
+extern "C" int tl_differential_combine(const float* maps, const void* gate, void* out, int out_dtype, int n_tokens,
+                                       int n_heads, int dv, float lam, float eps, float out_scale, void* stream) {
+    const long long rows = (long long)n_tokens * n_heads;
+    if (rows <= 0) return TL_OK;
+    if (dv <= 0) return TL_BAD_SIZE;
+    const dim3 grid((unsigned)((rows + 3) / 4)), block(128);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (out_dtype == TL_F32)
+        return (int)tl_launch(differential_combine_kernel<float>, grid, block, 0, s, maps, (const float*)gate, (float*)out, rows,
+                              n_heads, dv, lam, eps, out_scale);
+    if (out_dtype == TL_BF16)
+        return (int)tl_launch(differential_combine_kernel<__nv_bfloat16>, grid, block, 0, s, maps, (const __nv_bfloat16*)gate,
+                              (__nv_bfloat16*)out, rows, n_heads, dv, lam, eps, out_scale);
+    return TL_BAD_DTYPE;
+}

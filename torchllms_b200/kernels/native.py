@@ -151,7 +151,7 @@ class NativeOps:
     # ------------------------------------------------------------ libraries
     def prepare(self, dtype: torch.dtype, sampling: bool = True) -> None:
         """Compile, side by side, what a model of this dtype will call."""
-        names = ["elementwise", "sublayer", "rope", "attention", "gemm_simt"]
+        names = ["elementwise", "sublayer", "rope", "attention", "gemm_simt", "recurrent", "moe"]
         if dtype == torch.bfloat16:
             names += ["attention_mma", "attention_decode", "gemm_tcgen05"]
         if sampling:
@@ -283,11 +283,14 @@ class NativeOps:
         return out
 
     @_timed
-    def norm_add(self, h: torch.Tensor, delta, weight: torch.Tensor, eps: float, out_dtype: torch.dtype) -> torch.Tensor:
+    def norm_add(self, h: torch.Tensor, delta, weight: torch.Tensor, eps: float, out_dtype: torch.dtype,
+                 then_weight: Optional[torch.Tensor] = None, then_eps: float = 0.0) -> torch.Tensor:
         """``h += delta / sqrt(mean(delta^2) + eps) * weight`` in place (float32): the norm of a
         sublayer's output and the residual sum in one kernel.  ``delta`` is a tensor, float32
         partial sums ``[splits, T, dim]`` or a :class:`PendingProduct`.  Returns the new stream in
-        ``out_dtype`` (``h`` itself for float32)."""
+        ``out_dtype`` (``h`` itself for float32), or, with ``then_weight``, the RMS norm of the new
+        stream under that weight and ``then_eps`` (the norm in front of the next sublayer, from
+        the same kernel)."""
         if isinstance(delta, PendingProduct):
             delta = delta.take(self)
         _cuda_contig(h, "residual stream", torch.float32)
@@ -303,6 +306,16 @@ class NativeOps:
             splits, plane = delta.shape[0], delta.stride(0)
         else:
             _need(delta.shape == h.shape, "delta must have the stream's shape")
+        if then_weight is not None:
+            _cuda_contig(then_weight, "following norm's weight", torch.float32)
+            _need(then_weight.numel() == dim, "the following norm's weight must match the stream's width")
+            out = torch.empty((T, dim), dtype=out_dtype, device=h.device)
+            rc = self._lib("sublayer").tl_norm_add_norm(
+                _ptr(h), _ptr(delta), _DT[delta.dtype], splits, ctypes.c_longlong(plane), _ptr(weight), _ptr(then_weight),
+                _ptr(out), _DT[out_dtype], T, dim, ctypes.c_float(eps), ctypes.c_float(then_eps), _stream())
+            _check(rc, "norm_add_norm")
+            self.launches += 1
+            return out
         rows = None if out_dtype == torch.float32 else torch.empty((T, dim), dtype=out_dtype, device=h.device)
         rc = self._lib("sublayer").tl_norm_add(_ptr(h), _ptr(delta), _DT[delta.dtype], splits, ctypes.c_longlong(plane),
                                               _ptr(weight), _ptr(rows), T, dim, ctypes.c_float(eps), _stream())
@@ -432,6 +445,235 @@ class NativeOps:
         out = torch.empty((T, H, N), dtype=x.dtype, device=x.device)
         _check(self._lib("gemm_simt").tl_head_linear(_ptr(x), _ptr(w), _ptr(out), _DT[x.dtype], T, H, N, K, _stream()), "head_linear")
         self.launches += 1
+        return out
+
+    # ------------------------------------------- activations by name, depth average, map combination
+    _ACTS = {"silu": 0, "gelu_tanh": 1, "relu2": 2}
+
+    @_timed
+    def depth_mix(self, history: torch.Tensor, coef: torch.Tensor, n: int, out: torch.Tensor) -> torch.Tensor:
+        """``out = sum_j coef[j] * history[j]`` over the first ``n`` levels of ``history``
+        (float32 ``[levels, T, dim]``); ``out`` (``[T, dim]``) may be a later level of it."""
+        _cuda_contig(history, "history", torch.float32)
+        _cuda_contig(coef, "depth coefficients", torch.float32)
+        _cuda_contig(out, "depth_mix output", torch.float32)
+        _need(history.dim() == 3 and 1 <= n <= history.shape[0] and coef.numel() >= n and out.shape == history.shape[1:],
+              "depth_mix: history [levels, T, dim], n coefficients, out [T, dim]")
+        rc = self._lib("sublayer").tl_depth_mix(_ptr(history), ctypes.c_longlong(history.stride(0)), _ptr(coef), int(n), _ptr(out),
+                                               ctypes.c_longlong(out.numel()), _stream())
+        _check(rc, "depth_mix")
+        self.launches += 1
+        return out
+
+    def _act(self, x: torch.Tensor, kind: str, out_dtype: Optional[torch.dtype], gated: bool) -> torch.Tensor:
+        _need(kind in self._ACTS, f"unknown activation {kind!r}; known: {', '.join(self._ACTS)}")
+        _cuda_contig(x, "activation input")
+        _need(x.dim() in (2, 3) and x.dtype in _DT and (not gated or x.shape[-1] % 2 == 0),
+              "activation input must be [tokens, width] (gated: [tokens, 2 * hidden]) in float32/bfloat16")
+        splits = x.shape[0] if x.dim() == 3 else 1
+        _need(splits == 1 or x.dtype == torch.float32, "partial sums must be float32")
+        out_dtype = out_dtype or x.dtype
+        _need(out_dtype in _DT and (out_dtype == x.dtype or x.dtype == torch.float32), "an activation cannot widen bfloat16 input")
+        n, hidden = x.shape[-2], x.shape[-1] // (2 if gated else 1)
+        out = torch.empty((n, hidden), dtype=out_dtype, device=x.device)
+        rc = self._lib("sublayer").tl_act(_ptr(x), _DT[x.dtype], splits, ctypes.c_longlong(x.stride(0) if splits > 1 else 0),
+                                         _ptr(out), _DT[out_dtype], n, hidden, self._ACTS[kind], 1 if gated else 0, _stream())
+        _check(rc, "activation")
+        self.launches += 1
+        return out
+
+    @_timed
+    def activation(self, x: torch.Tensor, kind: str, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        """``act(x)`` by name (``silu``, ``gelu_tanh``, ``relu2``: the square of relu), float32 arithmetic;
+        ``x`` is ``[tokens, width]`` or float32 partial sums of it."""
+        return self._act(x, kind, out_dtype, False)
+
+    @_timed
+    def gated_act(self, gate_up: torch.Tensor, activation: str, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        """``act(gate) * up`` for rows ``[gate | up]`` (or float32 partial sums of them)."""
+        return self._act(gate_up, activation, out_dtype, True)
+
+    def linear_gated_act(self, x: torch.Tensor, w_gate_up: torch.Tensor, *, activation: str) -> torch.Tensor:
+        """The gate/up product over the stacked weight ``[2 H, K]`` and ``act(gate) * up``, in ``x``'s dtype."""
+        return self.gated_act(self.linear(x, w_gate_up, partials_ok=True), activation, out_dtype=x.dtype)
+
+    @_timed
+    def differential_combine(self, maps: torch.Tensor, lam: float, *, eps: float, out_scale: float,
+                             gate: Optional[torch.Tensor], out_dtype: torch.dtype) -> torch.Tensor:
+        """Two attention maps over the same values into one result: ``maps`` is float32 ``[T, 2 H, dv]``
+        with all first maps before all second maps; per (token, head) ``o = a1 - lam * a2``, then
+        ``o / sqrt(mean(o^2) + eps) * out_scale * gate[t, h]``.  Returns ``[T, H * dv]``."""
+        _cuda_contig(maps, "attention maps", torch.float32)
+        _need(maps.dim() == 3 and maps.shape[1] % 2 == 0 and out_dtype in _DT, "maps must be float32 [tokens, 2 * heads, dv]")
+        T, H, dv = maps.shape[0], maps.shape[1] // 2, maps.shape[2]
+        if gate is not None:
+            _cuda_contig(gate, "gate", out_dtype)
+            _need(gate.shape == (T, H), "gate must be [tokens, heads]")
+        out = torch.empty((T, H * dv), dtype=out_dtype, device=maps.device)
+        rc = self._lib("sublayer").tl_differential_combine(_ptr(maps), _ptr(gate), _ptr(out), _DT[out_dtype], T, H, dv,
+                                                          ctypes.c_float(lam), ctypes.c_float(eps), ctypes.c_float(out_scale),
+                                                          _stream())
+        _check(rc, "differential_combine")
+        self.launches += 1
+        return out
+
+    @_timed
+    def rope_store(self, proj: torch.Tensor, positions: torch.Tensor, table: torch.Tensor, *, n_q_heads: int, n_k_heads: int,
+                   n_v_heads: int, head_dim: int, v_head_dim: int, rot_dims: int, interleaved: bool, n_extra: int,
+                   k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor], slot_mapping: Optional[torch.Tensor],
+                   page_size: int, out_dtype: torch.dtype):
+        """What follows a stacked projection ``[q heads | k heads | v heads | extra]`` (``[T, width]`` or
+        float32 partial sums): the first ``rot_dims`` coordinates of every q and k head are rotated by
+        the position's angles (``table`` float32 ``[positions, rot_dims / 2, 2]``), k goes to
+        ``k_pages`` ``[pages, n_k_heads, page_size, head_dim]`` and v to ``v_pages`` ``[pages,
+        n_v_heads, page_size, v_head_dim]`` at ``slot_mapping``, and ``q [T, n_q_heads, head_dim]`` and
+        ``sigmoid(extra)`` come back in ``out_dtype``.  ``n_k_heads = n_v_heads = 0``: a run that reads
+        another run's cache."""
+        _cuda_contig(proj, "projection")
+        _cuda_contig(positions, "positions", torch.int32)
+        _cuda_contig(table, "rotary table", torch.float32)
+        width = (n_q_heads + n_k_heads) * head_dim + n_v_heads * v_head_dim + n_extra
+        _need(proj.dim() in (2, 3) and proj.shape[-1] == width and proj.dtype in _DT, "projection rows must be [q | k | v | extra]")
+        splits = proj.shape[0] if proj.dim() == 3 else 1
+        _need(splits == 1 or proj.dtype == torch.float32, "partial sums must be float32")
+        _need(out_dtype in _DT and (out_dtype == proj.dtype or proj.dtype == torch.float32), "rope_store cannot widen bfloat16 input")
+        _need(0 <= rot_dims <= head_dim and rot_dims % 2 == 0, "rot_dims must be even and at most head_dim")
+        _need(table.dim() == 3 and table.shape[2] == 2 and (rot_dims == 0 or table.shape[1] == rot_dims // 2),
+              "rotary table must be [positions, rot_dims / 2, 2]")
+        T = proj.shape[-2]
+        _need(positions.numel() == T, "one position per token")
+        if n_k_heads:
+            _cuda_contig(k_pages, "k_pages", out_dtype)
+            _cuda_contig(v_pages, "v_pages", out_dtype)
+            _cuda_contig(slot_mapping, "slot_mapping", torch.int32)
+            _need(k_pages.shape[1:] == (n_k_heads, page_size, head_dim) and v_pages.shape[1:] == (n_v_heads, page_size, v_head_dim)
+                  and v_pages.shape[0] == k_pages.shape[0], "pages must be [pages, heads, page_size, size] for keys and for values")
+            _need(slot_mapping.numel() == T, "one cache slot per token")
+            self._debug_limit("rope", 0, k_pages.shape[0])
+        else:
+            _need(n_v_heads == 0, "values are stored with keys")
+            k_pages = v_pages = None
+        q = torch.empty((T, n_q_heads, head_dim), dtype=out_dtype, device=proj.device)
+        extra = torch.empty((T, n_extra), dtype=out_dtype, device=proj.device) if n_extra else None
+        rc = self._lib("rope").tl_rope_store(
+            _ptr(proj), _DT[proj.dtype], splits, _ptr(positions), _ptr(table), _ptr(slot_mapping if k_pages is not None else None),
+            _ptr(q), _ptr(extra), _ptr(k_pages), _ptr(v_pages), _DT[out_dtype], T, n_q_heads, n_k_heads, n_v_heads, head_dim,
+            v_head_dim, rot_dims, n_extra, page_size, table.shape[0], 1 if interleaved else 0, _stream())
+        _check(rc, "rope_store")
+        self.launches += 1
+        return q, extra
+
+    # -------------------------------------------------------------- recurrence
+    @_timed
+    def mingru_scan(self, proj: torch.Tensor, bias: Optional[torch.Tensor], state: torch.Tensor, q_start: torch.Tensor,
+                    state_slot: torch.Tensor, fresh: torch.Tensor, *, n_seqs: int, max_q_len: int,
+                    out_dtype: torch.dtype) -> torch.Tensor:
+        """The minGRU recurrence over every request's portion.  ``proj`` is ``[T, 3 W]`` = ``[z | u | g]``
+        (or float32 partial sums), ``bias`` float32 ``[3 W]``; with ``a = sigmoid(z)`` and ``c = u + 1/2``
+        for ``u >= 0``, ``sigmoid(u)`` elsewhere: ``S <- (1 - a) S + a c`` and ``out = S * silu(g)``.
+        ``state`` (float32 ``[slots, W]``) holds every request's ``S`` at row ``state_slot[b]``: read
+        (as zero where ``fresh[b]``) and left as the portion's last token leaves it."""
+        _cuda_contig(proj, "projection")
+        _cuda_contig(state, "state", torch.float32)
+        for t, name in ((q_start, "q_start"), (state_slot, "state_slot"), (fresh, "fresh")):
+            _cuda_contig(t, name, torch.int32)
+        _need(proj.dim() in (2, 3) and proj.shape[-1] % 3 == 0 and proj.dtype in _DT, "projection rows must be [z | u | g]")
+        splits = proj.shape[0] if proj.dim() == 3 else 1
+        _need(splits == 1 or proj.dtype == torch.float32, "partial sums must be float32")
+        _need(out_dtype in _DT and (out_dtype == proj.dtype or proj.dtype == torch.float32), "mingru_scan cannot widen bfloat16 input")
+        T, W = proj.shape[-2], proj.shape[-1] // 3
+        _need(state.dim() == 2 and state.shape[1] == W, "state must be [slots, width]")
+        _need(q_start.numel() >= n_seqs + 1 and state_slot.numel() >= n_seqs and fresh.numel() >= n_seqs,
+              "q_start, state_slot and fresh must cover every request of the step")
+        if bias is not None:
+            _cuda_contig(bias, "bias", torch.float32)
+            _need(bias.numel() == 3 * W, "bias must have 3 * width elements")
+        lib = self._lib("recurrent")
+        lib.tl_mingru_scan_scratch.restype = ctypes.c_longlong
+        ws = self._scratch(proj.device, lib.tl_mingru_scan_scratch(n_seqs, W, max_q_len), "recurrent")
+        out = torch.empty((T, W), dtype=out_dtype, device=proj.device)
+        rc = lib.tl_mingru_scan(_ptr(proj), _DT[proj.dtype], splits, ctypes.c_longlong(proj.stride(0) if splits > 1 else 0),
+                                _ptr(bias), _ptr(state), _ptr(q_start), _ptr(state_slot), _ptr(fresh), _ptr(out), _DT[out_dtype],
+                                T, n_seqs, W, max_q_len, _ptr(ws), _stream())
+        _check(rc, "mingru_scan")
+        self.launches += 2 if max_q_len > 64 else 1
+        return out
+
+    # ----------------------------------------------------------------- experts
+    @_timed
+    def moe_route(self, x: torch.Tensor, w_router: torch.Tensor, correction: Optional[torch.Tensor], *, n_experts: int,
+                  top: int, scale: float, renormalize: bool, shared_gate: bool):
+        """Router of a layer of experts: ``s = softmax(w_router[:E] x)`` in float32, the ``top`` experts
+        with the largest ``s + correction`` chosen, weights ``s * scale`` (over their sum with
+        ``renormalize``); with ``shared_gate`` the row ``w_router[E]`` gives ``sigmoid(.)`` per token.
+        Returns ``(chosen int32 [T, top], weights float32 [T, top], gate float32 [T] or None)``."""
+        _cuda_contig(x, "router input")
+        _cuda_contig(w_router, "router weight", torch.float32)
+        _need(x.dim() == 2 and x.dtype in _DT and w_router.dim() == 2 and w_router.shape[1] == x.shape[1]
+              and w_router.shape[0] == n_experts + (1 if shared_gate else 0), "router: x [T, dim] against w [E (+ 1), dim]")
+        if correction is not None:
+            _cuda_contig(correction, "correction", torch.float32)
+            _need(correction.numel() == n_experts, "one correction per expert")
+        T = x.shape[0]
+        chosen = torch.empty((T, top), dtype=torch.int32, device=x.device)
+        weights = torch.empty((T, top), dtype=torch.float32, device=x.device)
+        gate = torch.empty((T,), dtype=torch.float32, device=x.device) if shared_gate else None
+        rc = self._lib("moe").tl_moe_route(_ptr(x), _DT[x.dtype], _ptr(w_router), _ptr(correction), _ptr(chosen), _ptr(weights),
+                                          _ptr(gate), T, x.shape[1], n_experts, top, ctypes.c_float(scale),
+                                          1 if renormalize else 0, _stream())
+        _check(rc, "moe_route")
+        self.launches += 1
+        return chosen, weights, gate
+
+    @_timed
+    def moe_experts(self, x: torch.Tensor, chosen: torch.Tensor, weights: torch.Tensor, w_up: torch.Tensor,
+                    w_down: torch.Tensor, *, activation: str, shared: Optional[torch.Tensor] = None,
+                    shared_gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``out[t] = sum_k weights[t, k] * down_e(act(up_e x[t]))`` with ``e = chosen[t, k]``, plus
+        ``shared[t]`` (``[T, dim]`` or float32 partial sums) times ``shared_gate[t]`` where given.
+        ``w_up`` is ``[E, hidden, dim]``, ``w_down`` ``[E, dim, hidden]``.  The (token, choice) pairs are
+        sorted by expert on the device and both products run grouped over the sorted rows."""
+        _cuda_contig(x, "experts' input")
+        _cuda_contig(chosen, "chosen", torch.int32)
+        _cuda_contig(weights, "weights", torch.float32)
+        _cuda_contig(w_up, "experts' up weights", x.dtype)
+        _cuda_contig(w_down, "experts' down weights", x.dtype)
+        _need(activation in self._ACTS, f"unknown activation {activation!r}")
+        _need(x.dim() == 2 and x.dtype in _DT and chosen.dim() == 2 and chosen.shape == weights.shape and chosen.shape[0] == x.shape[0],
+              "experts: x [T, dim], chosen and weights [T, top]")
+        T, dim = x.shape
+        top = chosen.shape[1]
+        E, hidden = w_up.shape[0], w_up.shape[1]
+        _need(w_up.shape == (E, hidden, dim) and w_down.shape == (E, dim, hidden), "experts: w_up [E, hidden, dim], w_down [E, dim, hidden]")
+        lib = self._lib("moe")
+        pairs = T * top
+        max_tiles = lib.tl_moe_max_tiles(pairs, E)
+        index = torch.empty(2 * pairs + 1 + 3 * max_tiles, dtype=torch.int32, device=x.device)
+        order, place, tiles = index[:pairs], index[pairs:2 * pairs], index[2 * pairs:]
+        _check(lib.tl_moe_plan(_ptr(chosen), pairs, E, _ptr(order), _ptr(place), _ptr(tiles), _stream()), "moe_plan")
+        u = torch.empty((pairs, hidden), dtype=x.dtype, device=x.device)
+        _check(lib.tl_moe_gemm(_ptr(x), _ptr(w_up), _ptr(u), _DT[x.dtype], _ptr(tiles), _ptr(order), top, pairs, E, hidden, dim,
+                               self._ACTS[activation], _stream()), "moe_gemm (up)")
+        y = torch.empty((pairs, dim), dtype=x.dtype, device=x.device)
+        _check(lib.tl_moe_gemm(_ptr(u), _ptr(w_down), _ptr(y), _DT[x.dtype], _ptr(tiles), _ptr(order), 0, pairs, E, dim, hidden,
+                               -1, _stream()), "moe_gemm (down)")
+        splits, plane = 1, 0
+        if shared is not None:
+            _cuda_contig(shared, "shared expert's output")
+            _need(shared.dtype in _DT and shared.shape[-2:] == (T, dim), "shared must be [T, dim] or partial sums of it")
+            if shared.dim() == 3:
+                _need(shared.dtype == torch.float32, "partial sums must be float32")
+                splits, plane = shared.shape[0], shared.stride(0)
+            _need(shared.dtype == x.dtype or (shared.dtype == torch.float32 and x.dtype == torch.bfloat16), "shared: dtype")
+        if shared_gate is not None:
+            _cuda_contig(shared_gate, "shared gate", torch.float32)
+            _need(shared is not None and shared_gate.numel() == T, "one gate value per token, with a shared expert")
+        out = torch.empty((T, dim), dtype=x.dtype, device=x.device)
+        rc = lib.tl_moe_combine(_ptr(y), _DT[x.dtype], _ptr(place), _ptr(weights), _ptr(shared),
+                                _DT[shared.dtype] if shared is not None else 0, splits, ctypes.c_longlong(plane), _ptr(shared_gate),
+                                _ptr(out), T, dim, top, _stream())
+        _check(rc, "moe_combine")
+        self.launches += 4
         return out
 
     def can_fuse_residual(self, pending, h: torch.Tensor) -> bool:
@@ -705,7 +947,8 @@ class NativeOps:
                         impl: str = "auto", n_tokens: Optional[int] = None,
                         out: Optional[torch.Tensor] = None, keep_first: int = 0,
                         distance_bias: Optional[torch.Tensor] = None, distance_buckets: Optional[torch.Tensor] = None,
-                        gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+                        gate: Optional[torch.Tensor] = None, n_v_heads: Optional[int] = None,
+                        out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         """``impl``: ``"general"`` (CUDA cores, any supported size, both dtypes), ``"mma"`` (tensor
         cores, bfloat16, head_dim 16/32/64/128), ``"decode"`` (tensor cores fed by TMA, bfloat16,
         head_dim 64/128, steps whose requests bring one token or very few), ``"prefill"``
@@ -724,13 +967,16 @@ class NativeOps:
         ``[T, H, v_dim]``), ``keep_first`` (with a window: the first so many keys of a request stay
         visible), ``distance_bias`` ``[rows, H]`` float32 with ``distance_buckets`` (int32: the
         table's row for every distance), added to the scaled score, and ``gate`` (``[T, H]`` or
-        ``[T, H * v_dim]``, in q's dtype), by which the result is multiplied."""
+        ``[T, H * v_dim]``, in q's dtype), by which the result is multiplied; ``n_v_heads`` (``v_pages`` has
+        fewer heads than ``k_pages``: key head ``j`` goes with value head ``j % n_v_heads``, several maps
+        with keys of their own over one set of values) and ``out_dtype=torch.float32`` (the result
+        leaves unrounded whatever q's dtype)."""
         if keep_first or distance_bias is not None or gate is not None or v_pages.shape[-1] != q.shape[-1] \
-                or q.shape[-1] % 16 != 0:
+                or q.shape[-1] % 16 != 0 or v_pages.shape[1] != k_pages.shape[1] or out_dtype not in (None, q.dtype):
             _need(impl in ("auto", "general", "mma"), "only the general and the mma.sync attention kernels take these options")
             return self._paged_attention_general(q, k_pages, v_pages, block_table, q_start, kv_len, n_seqs, max_q_len,
                                                  max_kv_len, scale, window, page_size, allow_split, n_tokens, out,
-                                                 keep_first, distance_bias, distance_buckets, gate, impl)
+                                                 keep_first, distance_bias, distance_buckets, gate, impl, n_v_heads, out_dtype)
         _cuda_contig(q, "q")
         _cuda_contig(k_pages, "k_pages", q.dtype)
         _cuda_contig(v_pages, "v_pages", q.dtype)
@@ -821,11 +1067,12 @@ class NativeOps:
     class _AttentionOptions(ctypes.Structure):
         _fields_ = [("v_head_dim", ctypes.c_int), ("keep_first", ctypes.c_int), ("rel", ctypes.c_void_p),
                     ("bucket", ctypes.c_void_p), ("n_bucket", ctypes.c_int), ("gate", ctypes.c_void_p),
-                    ("gate_mode", ctypes.c_int)]
+                    ("gate_mode", ctypes.c_int), ("n_v_heads", ctypes.c_int), ("out_f32", ctypes.c_int)]
 
     def _paged_attention_general(self, q, k_pages, v_pages, block_table, q_start, kv_len, n_seqs, max_q_len, max_kv_len,
                                  scale, window, page_size, allow_split, n_tokens, out, keep_first, distance_bias,
-                                 distance_buckets, gate, impl: str = "general") -> torch.Tensor:
+                                 distance_buckets, gate, impl: str = "general", n_v_heads: Optional[int] = None,
+                                 out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         """The CUDA-core kernel with everything it can do (see :meth:`paged_attention`), or, with
         ``impl`` "auto" or "mma", in bfloat16 and for sizes it takes (keys and values multiples of 8
         up to 128), the extended form of the mma.sync kernel, which does the same."""
@@ -841,18 +1088,24 @@ class NativeOps:
         _need(0 < T <= T_all, "n_tokens must lie within q")
         n_kv_heads, v_dim = k_pages.shape[1], v_pages.shape[3]
         self.check_attention_sizes(n_heads, n_kv_heads, head_dim, q.dtype, v_dim)
-        _need(k_pages.shape[2] == page_size and k_pages.shape[3] == head_dim and v_pages.shape[:3] == k_pages.shape[:3],
-              "pages must be [pages, n_kv_heads, page_size, head_dim] (values: their own last size)")
+        v_heads = v_pages.shape[1]
+        _need(n_v_heads in (None, v_heads) and n_kv_heads % v_heads == 0, "n_v_heads must be the heads of v_pages and divide the key heads")
+        _need(k_pages.shape[2] == page_size and k_pages.shape[3] == head_dim and v_pages.shape[0] == k_pages.shape[0]
+              and v_pages.shape[2] == page_size,
+              "pages must be [pages, n_kv_heads, page_size, head_dim] (values: their own head count and last size)")
+        out_dtype = out_dtype or q.dtype
+        _need(out_dtype in (q.dtype, torch.float32), "attention writes q's dtype or float32")
         _need(block_table.shape[0] >= n_seqs and q_start.numel() >= n_seqs + 1 and kv_len.numel() >= n_seqs,
               "block_table, q_start and kv_len must cover every request of the step")
         _need(block_table.shape[1] * page_size >= max_kv_len, "block_table is too narrow for max_kv_len")
         _need(keep_first >= 0 and (not keep_first or window), "keep_first goes with a window")
         if out is None:
-            out = torch.empty((T_all, n_heads, v_dim), dtype=q.dtype, device=q.device)
+            out = torch.empty((T_all, n_heads, v_dim), dtype=out_dtype, device=q.device)
         else:
-            _cuda_contig(out, "out", q.dtype)
+            _cuda_contig(out, "out", out_dtype)
             _need(out.shape == (T_all, n_heads, v_dim), "out must be [tokens, heads, v_dim]")
-        opt = self._AttentionOptions(v_dim, int(keep_first), None, None, 0, None, 0)
+        opt = self._AttentionOptions(v_dim, int(keep_first), None, None, 0, None, 0, v_heads,
+                                     1 if (out_dtype == torch.float32 and q.dtype != torch.float32) else 0)
         if distance_bias is not None:
             _cuda_contig(distance_bias, "distance_bias", torch.float32)
             _cuda_contig(distance_buckets, "distance_buckets", torch.int32)
