@@ -269,33 +269,75 @@ DESIGN_SIZES = {
 }
 
 
-def design_workload(args, peaks):
-    """Nagolix beside the Llama decoder at equal sizes (random weights, bfloat16): for every size
-    of ``DESIGN_SIZES`` the prefill of one 2,048-token prompt and decode steps at batch 8 behind
-    2,048-token prompts, timed with CUDA events on the step function, and where each model's time goes
-    (per kernel-library call, from ``ops.profile()``).  Nagolix layers alternate latent attention,
-    attention, latent attention reading the first one's latents, attention."""
+# Rakuvik at sizes that resemble a real model's layers: a minGRU layer with a dense feed-forward, differential
+# attention with experts, a minGRU layer with experts, differential attention reading the first one's keys and values
+RAKUVIK_SIZES = {
+    "w2048": dict(dim=2048, heads=16, kv_heads=4, head_dim=128, map_dim=64, rot_dims=64, gru_width=2048, ff=8192,
+                  experts=16, top=4, expert_ff=2048, shared_ff=2048, layers=4),
+    "w4096": dict(dim=4096, heads=32, kv_heads=8, head_dim=128, map_dim=64, rot_dims=64, gru_width=4096, ff=14336,
+                  experts=32, top=4, expert_ff=3584, shared_ff=3584, layers=4),
+}
+
+
+def _nagolix_config(z, vocab, max_len):
+    from torchllms_b200.models.nagolix import LayerConfig, MixerConfig, MlpConfig, NagolixConfig
+    hd = z["head_dim"]
+    att = MixerConfig("attention", z["heads"], hd, hd, hd ** -0.5, z["window"], z["keep_first"], z["kv_heads"], 4096.0)
+    lat = MixerConfig("latent_attention", z["heads"], hd, hd, hd ** -0.5, z["window"], kv_rank=z["rank"])
+    lat2 = MixerConfig("latent_attention", z["heads"], hd, hd, hd ** -0.5, z["window"], kv_rank=z["rank"], kv_from=0)
+    mlp = MlpConfig("dense", z["ff"], 7.0)
+    kinds = [lat, att, lat2, att]
+    return NagolixConfig("Nagolix", vocab, z["dim"], max_len, 1e-6, 1.0,
+                         tuple(LayerConfig(kinds[i % 4], mlp) for i in range(z["layers"])))
+
+
+def _rakuvik_config(z, vocab, max_len):
+    from torchllms_b200.models.rakuvik import AttentionConfig, LayerConfig, MinGruConfig, MlpConfig, RakuvikConfig
+    att = AttentionConfig(heads=z["heads"], kv_heads=z["kv_heads"], dim=z["map_dim"], vdim=z["head_dim"], scale=z["map_dim"] ** -0.5,
+                          diff=0.5, rot_dims=z["rot_dims"], rot_base=500000.0, rot_factor=8.0)
+    att2 = AttentionConfig(heads=z["heads"], kv_heads=z["kv_heads"], dim=z["map_dim"], vdim=z["head_dim"], scale=z["map_dim"] ** -0.5,
+                           diff=0.5, rot_dims=z["rot_dims"], rot_base=500000.0, rot_factor=8.0, kv_from=1)
+    gru = MinGruConfig(width=z["gru_width"])
+    dense = MlpConfig("dense", z["ff"])
+    moe = MlpConfig("moe", z["expert_ff"], experts=z["experts"], top=z["top"], router_scale=1.5, shared_ff=z["shared_ff"])
+    kinds = [(gru, dense), (att, moe), (gru, moe), (att2, moe)]
+    if z["layers"] % 4:
+        raise ValueError("the Rakuvik workload's layers come in fours")
+    layers = []
+    for i in range(z["layers"]):
+        mixer, mlp = kinds[i % 4]
+        if i % 4 == 3:
+            mixer = AttentionConfig(**{**mixer.__dict__, "kv_from": i - 2})
+        layers.append(LayerConfig(mixer, mlp))
+    return RakuvikConfig("Rakuvik", vocab, z["dim"], 1e-6, tuple(layers), max_seq_len=max_len)
+
+
+DESIGNS = {"nagolix": ("Nagolix", DESIGN_SIZES, _nagolix_config), "rakuvik": ("Rakuvik", RAKUVIK_SIZES, _rakuvik_config)}
+
+
+def design_workload(args, peaks, design="nagolix"):
+    """A design beside the Llama decoder at equal width, heads, feed-forward width and depth (random weights,
+    bfloat16): for every size of the design's table the prefill of one 2,048-token prompt and decode steps
+    at batch 8 behind 2,048-token prompts, timed with CUDA events on the step function, and where each
+    model's time goes (per kernel-library call, from ``ops.profile()``).  Nagolix layers alternate latent
+    attention, attention, latent attention reading the first one's latents, attention; Rakuvik layers
+    alternate minGRU with a dense feed-forward, differential attention with experts, minGRU with experts,
+    differential attention reading the first one's keys and values with experts."""
     import torch
     from torchllms_b200.engine.step import StepEntry
     from torchllms_b200.inference import LLM
     from torchllms_b200.models.llama_config import LlamaConfig, RopeScaling
-    from torchllms_b200.models.nagolix import LayerConfig, MixerConfig, MlpConfig, NagolixConfig
 
+    title, sizes, make_config = DESIGNS[design]
     vocab, prompt_len, batch = 32000, PROMPT_LEN, args.batch
     steps, warmup = min(args.steps, 64), max(args.warmup, 3)
     max_len = prompt_len + warmup + steps + 64
     gen = torch.Generator().manual_seed(7)
     out = {}
-    for name, z in DESIGN_SIZES.items():
+    for name, z in sizes.items():
         hd = z["head_dim"]
-        att = MixerConfig("attention", z["heads"], hd, hd, hd ** -0.5, z["window"], z["keep_first"], z["kv_heads"], 4096.0)
-        lat = MixerConfig("latent_attention", z["heads"], hd, hd, hd ** -0.5, z["window"], kv_rank=z["rank"])
-        lat2 = MixerConfig("latent_attention", z["heads"], hd, hd, hd ** -0.5, z["window"], kv_rank=z["rank"], kv_from=0)
-        mlp = MlpConfig("dense", z["ff"], 7.0)
-        kinds = [lat, att, lat2, att]
         configs = {
-            "nagolix": NagolixConfig("Nagolix", vocab, z["dim"], max_len, 1e-6, 1.0,
-                                     tuple(LayerConfig(kinds[i % 4], mlp) for i in range(z["layers"]))),
+            design: make_config(z, vocab, max_len),
             "llama": LlamaConfig(architecture="LlamaForCausalLM", n_layers=z["layers"], dim=z["dim"], n_heads=z["heads"],
                                  n_kv_heads=z["kv_heads"], head_dim=hd, ffn_hidden=z["ff"], vocab_size=vocab, norm_eps=1e-5,
                                  rope_theta=500000.0, rope_scaling=RopeScaling(), tie_word_embeddings=True, max_seq_len=max_len),
@@ -359,10 +401,10 @@ def design_workload(args, peaks):
             }
             del llm, engine
             torch.cuda.empty_cache()
-    return {"metric": "Nagolix beside Llama at equal sizes: prefill and decode tokens/s", "unit": "tokens/s", "n_gpus": 1,
+    return {"metric": f"{title} beside Llama at equal sizes: prefill and decode tokens/s", "unit": "tokens/s", "n_gpus": 1,
             "dtype": "bf16", "data": "synthetic (uniform random token ids, random weights)",
             "config": {"prompt_len": prompt_len, "batch": batch, "decode_steps": steps, "warmup": warmup, "vocab": vocab,
-                       "sizes": DESIGN_SIZES}, "sizes": out, "peaks": peaks["source"]}
+                       "sizes": sizes}, "sizes": out, "peaks": peaks["source"]}
 
 
 def main():
@@ -374,9 +416,9 @@ def main():
     ap.add_argument("--layers", type=int, default=SHAPE_8B["n_layers"], help="fewer layers than the shape has (named in config)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--skip-points", action="store_true", help="only the headline batch and the prefill")
-    ap.add_argument("--workload", default="decode_8b", choices=["decode_8b", "design_nagolix"] + sorted(SERVE),
+    ap.add_argument("--workload", default="decode_8b", choices=["decode_8b", "design_nagolix", "design_rakuvik"] + sorted(SERVE),
                     help="decode_8b: the headline (default); serve_1b, long_3b: whole serving runs through LLM.generate; "
-                         "design_nagolix: the Nagolix design beside the Llama decoder at equal sizes")
+                         "design_nagolix, design_rakuvik: that design beside the Llama decoder at equal sizes")
     ap.add_argument("--context-len", type=int, default=PROMPT_LEN,
                     help="prompt length of the decode measurements (the headline is 2,048; the prefill figure stays at 2,048)")
     ap.add_argument("--long-contexts", type=lambda t: [int(x) for x in t.split(",") if x], default=[8192, 32768],
@@ -393,8 +435,8 @@ def main():
         return 2
     if args.impl == "reference":
         return reference_arm(args)
-    if args.workload == "design_nagolix":
-        print(json.dumps(design_workload(args, load_peaks())))
+    if args.workload.startswith("design_"):
+        print(json.dumps(design_workload(args, load_peaks(), args.workload[len("design_"):])))
         return 0
     if args.workload != "decode_8b":
         print(json.dumps(serving_workload(args, load_peaks())))

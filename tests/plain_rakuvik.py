@@ -121,17 +121,26 @@ def squared_relu_expert(h: torch.Tensor, up: torch.Tensor, down: torch.Tensor, r
     return _lin(_round(y, rounding), down, rounding)
 
 
-def route(h: torch.Tensor, w: Mapping[str, torch.Tensor], top: int, scale: float, rounding) -> Tuple[torch.Tensor, torch.Tensor]:
+def route(h: torch.Tensor, w: Mapping[str, torch.Tensor], top: int, scale: float, rounding,
+          margins: Optional[list] = None) -> Tuple[torch.Tensor, torch.Tensor]:
     """Chosen experts ``[n, top]`` and their weights: scores are a softmax over all experts, the
-    choice adds a correction that the weights do not carry, and nothing is renormalised."""
+    choice adds a correction that the weights do not carry, and nothing is renormalised.
+    ``margins`` collects, per token, how far the last chosen expert stood above the first one
+    left out, as a share of the larger of their two scores (rounding moves a score by a share of
+    itself; a test that wants no close call looks at this)."""
     s = torch.softmax(_round(h, rounding) @ w["router"].to(F).T, dim=-1)
-    chosen = torch.topk(s + w["correction"].to(F), top, dim=-1).indices
+    choice = s + w["correction"].to(F)
+    chosen = torch.topk(choice, top, dim=-1).indices
+    if margins is not None and top < choice.shape[1]:
+        best = torch.topk(choice, top + 1, dim=-1)
+        near = torch.gather(s, 1, best.indices[:, top - 1:top + 1]).max(-1).values
+        margins.append((best.values[:, top - 1] - best.values[:, top]) / near)
     return chosen, torch.gather(s, 1, chosen) * scale
 
 
-def moe_ff(h: torch.Tensor, w: Mapping[str, torch.Tensor], mlp: Mapping, rounding) -> torch.Tensor:
+def moe_ff(h: torch.Tensor, w: Mapping[str, torch.Tensor], mlp: Mapping, rounding, margins: Optional[list] = None) -> torch.Tensor:
     r = mlp["router"]
-    chosen, weights = route(h, w, r["top"], r["scale"], rounding)
+    chosen, weights = route(h, w, r["top"], r["scale"], rounding, margins)
     out = torch.zeros(h.shape[0], w["e0.down"].shape[0], dtype=F)
     for e in range(r["experts"]):
         for slot in range(r["top"]):
@@ -150,8 +159,8 @@ def _sub(tensors: Mapping[str, torch.Tensor], prefix: str) -> Dict[str, torch.Te
 
 
 def forward(config: Mapping, tensors: Mapping[str, torch.Tensor], tokens: List[int], rounding=None,
-            return_layers: bool = False):
-    """Logits ``[n, vocab]`` (float64) of every position of one sequence."""
+            return_layers: bool = False, margins: Optional[list] = None):
+    """Logits ``[n, vocab]`` (float64) of every position of one sequence.  ``margins``: see :func:`route`."""
     eps = config["norm"]["eps"]
     x = tensors["embed"].to(F)[torch.tensor(tokens, dtype=torch.long)]
     history = [x]
@@ -173,7 +182,7 @@ def forward(config: Mapping, tensors: Mapping[str, torch.Tensor], tokens: List[i
         if layer.get("mlp") is not None:
             fw = _sub(tensors, p + "mlp.")
             hin = scalar_norm(x, tensors[p + "norm2"], eps)
-            y = dense_ff(hin, fw, rounding) if layer["mlp"]["kind"] == "dense" else moe_ff(hin, fw, layer["mlp"], rounding)
+            y = dense_ff(hin, fw, rounding) if layer["mlp"]["kind"] == "dense" else moe_ff(hin, fw, layer["mlp"], rounding, margins)
             x = x + scalar_norm(y, tensors[p + "norm2b"], eps)
         history.append(x)
         coef = tensors[p + "dwa"].to(F)

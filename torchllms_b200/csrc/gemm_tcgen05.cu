@@ -197,7 +197,7 @@ struct GemmParams {
     int in_parts;
     float in_inv_dim, in_eps;
     // gated form: which gate.  0: silu(g) * u.  1: the clamped form, g = min(g, limit), u = clamp(u, -limit, limit),
-    // g * sigmoid(alpha * g) * (u + up_offset)
+    // g * sigmoid(alpha * g) * (u + up_offset).  2: gelu(g) * u, gelu in its tanh form
     int act_kind;
     float act_limit, act_alpha, act_up_offset;
     // residual form
@@ -440,6 +440,8 @@ __global__ void __launch_bounds__(NTHREADS) gemm_tcgen05_kernel(const __grid_con
                                 float y;
                                 if (p.act_kind == 0) {
                                     y = __fdividef(g, 1.f + __expf(-g)) * u;
+                                } else if (p.act_kind == 2) {
+                                    y = 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;
                                 } else {
                                     g = fminf(g, p.act_limit);
                                     u = fminf(fmaxf(u, -p.act_limit), p.act_limit);
@@ -774,6 +776,12 @@ extern "C" int tl_gemm_tcgen05_gated(const void* A, const void* W, void* out, in
                                      const float* in_ssq, int in_parts, float in_inv_dim, float in_eps, int* status,
                                      void* stream) {
     return gemm_gated(A, W, out, M, hidden, K, in_ssq, in_parts, in_inv_dim, in_eps, 0, 0.f, 0.f, 0.f, status, stream);
+}
+
+// The same product with gelu(gate) * up in its epilogue, gelu(z) = 0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3))).
+extern "C" int tl_gemm_tcgen05_gated_gelu(const void* A, const void* W, void* out, int M, int hidden, int K, int* status,
+                                          void* stream) {
+    return gemm_gated(A, W, out, M, hidden, K, nullptr, 0, 0.f, 0.f, 2, 0.f, 0.f, 0.f, status, stream);
 }
 
 // The same product with the clamped gate in its epilogue:

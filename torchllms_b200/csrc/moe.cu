@@ -1,7 +1,8 @@
 // Feed-forwards made of many small experts of which every token uses a few, routed on the device.
 //
-// route:    z = W_router x (float32; W_router may carry one more row, the shared expert's gate),
-//           s = softmax(z) over the experts, the `top` experts with the largest s + correction
+// logits:   z = W_router x (float32; W_router may carry one more row, the shared expert's gate), a warp per
+//           (token, row) for the few tokens of a decode step
+// select:   s = softmax(z) over the experts, the `top` experts with the largest s + correction
 //           are chosen (the lower index wins a tie), their weights are s * scale (divided by their
 //           sum first when renormalising); the extra row leaves as sigmoid(z).
 // plan:     the (token, choice) pairs sorted by expert, stably: for every expert where its rows
@@ -27,43 +28,70 @@ __device__ __forceinline__ float act_apply(float x, int act) {
     return r * r;
 }
 
-// One CTA per token.  Shared memory: the token's row as float32, then the scores.
+// Router logits of few tokens: grid (tokens, chunks of rows); the token's row in shared memory as float32,
+// a warp per router row, sixteen bytes of the row per lane and turn.
 template <typename T>
-__global__ void __launch_bounds__(128) moe_route_kernel(const T* __restrict__ x, const float* __restrict__ w_router,
-                                                        const float* __restrict__ correction, int* __restrict__ chosen,
-                                                        float* __restrict__ weights, float* __restrict__ gate, int dim,
-                                                        int n_experts, int n_rows, int top, float scale, int renormalize) {
-    extern __shared__ __align__(16) float sm[];
-    float* xs = sm;                 // [dim]
-    float* sc = sm + dim;           // [n_rows] logits, then scores
-    float* ch = sc + n_rows;        // [n_experts] what the choice looks at
+__global__ void __launch_bounds__(256) moe_logits_kernel(const T* __restrict__ x, const float* __restrict__ w_router,
+                                                         float* __restrict__ logits, int dim, int n_rows) {
+    extern __shared__ __align__(16) float xs[];
     grid_launch_dependents();
     grid_dependency_wait();
     const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
     for (int d = threadIdx.x; d < dim; d += blockDim.x) xs[d] = to_float(x[(size_t)t * dim + d]);
     __syncthreads();
-    for (int e = warp; e < n_rows; e += n_warps) {
-        const float* wr = w_router + (size_t)e * dim;
-        float acc = 0.f;
-        for (int d = lane; d < dim; d += 32) acc = fmaf(xs[d], wr[d], acc);
-        acc = warp_sum(acc);
-        if (lane == 0) sc[e] = acc;
+    const int e = blockIdx.y * n_warps + warp;
+    if (e >= n_rows) return;
+    const float* wr = w_router + (size_t)e * dim;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    if (dim % 4 == 0 && (((size_t)w_router) & 15u) == 0) {
+        int d = lane * 4;
+        for (; d + 3 * 128 < dim; d += 4 * 128) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float4 w = *reinterpret_cast<const float4*>(wr + d + j * 128);
+                const float4 v = *reinterpret_cast<const float4*>(xs + d + j * 128);
+                acc[j] = fmaf(v.x, w.x, fmaf(v.y, w.y, fmaf(v.z, w.z, fmaf(v.w, w.w, acc[j]))));
+            }
+        }
+        for (; d < dim; d += 128) {
+            const float4 w = *reinterpret_cast<const float4*>(wr + d);
+            const float4 v = *reinterpret_cast<const float4*>(xs + d);
+            acc[0] = fmaf(v.x, w.x, fmaf(v.y, w.y, fmaf(v.z, w.z, fmaf(v.w, w.w, acc[0]))));
+        }
+    } else {
+        for (int d = lane; d < dim; d += 32) acc[0] = fmaf(xs[d], wr[d], acc[0]);
     }
-    __syncthreads();
-    if (warp != 0) return;
+    const float total = warp_sum((acc[0] + acc[1]) + (acc[2] + acc[3]));
+    if (lane == 0) logits[(size_t)t * n_rows + e] = total;
+}
+
+// From the logits to the choice: a warp per token.  Shared memory per warp: scores, then what the choice looks at.
+__global__ void __launch_bounds__(128) moe_select_kernel(const float* __restrict__ logits, const float* __restrict__ correction,
+                                                         int* __restrict__ chosen, float* __restrict__ weights,
+                                                         float* __restrict__ gate, int n_tokens, int n_experts, int n_rows,
+                                                         int top, float scale, int renormalize) {
+    extern __shared__ float sm[];
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+    if (t >= n_tokens) return;
+    float* sc = sm + (size_t)warp * 2 * n_experts;
+    float* ch = sc + n_experts;
+    const float* z = logits + (size_t)t * n_rows;
     float mx = -INFINITY;
-    for (int e = lane; e < n_experts; e += 32) mx = fmaxf(mx, sc[e]);
+    for (int e = lane; e < n_experts; e += 32) mx = fmaxf(mx, z[e]);
     mx = warp_max(mx);
     float sum = 0.f;
-    for (int e = lane; e < n_experts; e += 32) sum += expf(sc[e] - mx);
+    for (int e = lane; e < n_experts; e += 32) sum += expf(z[e] - mx);
     sum = warp_sum(sum);
     const float inv = 1.f / sum;
     for (int e = lane; e < n_experts; e += 32) {
-        const float s = expf(sc[e] - mx) * inv;
+        const float s = expf(z[e] - mx) * inv;
         sc[e] = s;
         ch[e] = s + (correction != nullptr ? correction[e] : 0.f);
     }
-    if (lane == 0 && gate != nullptr) gate[t] = 1.f / (1.f + expf(-sc[n_experts]));
+    if (lane == 0 && gate != nullptr) gate[t] = 1.f / (1.f + expf(-z[n_experts]));
     __syncwarp();
     float total = 0.f;
     for (int k = 0; k < top; ++k) {
@@ -97,7 +125,7 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const T* __restrict__ x,
 // One CTA.  counts/offsets live in shared memory ([n_experts + 1] ints each).
 __global__ void __launch_bounds__(1024) moe_plan_kernel(const int* __restrict__ chosen, int n_pairs, int n_experts, int tile_rows,
                                                         int* __restrict__ order, int* __restrict__ place,
-                                                        int* __restrict__ tiles, int max_tiles) {
+                                                        int* __restrict__ tiles, int max_tiles, int* __restrict__ ends) {
     extern __shared__ int ism[];
     int* counts = ism;                    // [n_experts]
     int* offsets = ism + n_experts;       // [n_experts + 1]
@@ -121,6 +149,7 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(const int* __restrict__ 
                 ++n_tiles;
             }
             off += counts[e];
+            if (ends != nullptr) ends[e] = off;
         }
         offsets[n_experts] = off;
         tiles[0] = n_tiles;
@@ -151,7 +180,7 @@ constexpr int BN = 64, BK = 16, PAD = 4, NT = 256;
 template <typename T, typename TO, int BM>
 __global__ void __launch_bounds__(NT) moe_gemm_kernel(const T* __restrict__ A, const T* __restrict__ W, TO* __restrict__ C,
                                                       const int* __restrict__ tiles, const int* __restrict__ order,
-                                                      int gather_div, int N, int K, int act) {
+                                                      int gather_div, int N, int K, int act, long long w_expert, long long ldw) {
     constexpr int TM = BM / 16;
     __shared__ float As[BK][BM + PAD];
     __shared__ float Ws[BK][BN + PAD];
@@ -165,7 +194,7 @@ __global__ void __launch_bounds__(NT) moe_gemm_kernel(const T* __restrict__ A, c
     const int n0 = blockIdx.x * BN;
     for (int r = tid; r < BM; r += NT) src[r] = r < n_rows ? (gather_div > 0 ? order[row0 + r] / gather_div : row0 + r) : -1;
     __syncthreads();
-    W += (size_t)e * N * K;
+    W += (size_t)e * w_expert;
     const int lrow = tid >> 2, lk = (tid & 3) * 4;       // loads: a row (of 64) and four k
     float acc[TM][4];
 #pragma unroll
@@ -179,7 +208,7 @@ __global__ void __launch_bounds__(NT) moe_gemm_kernel(const T* __restrict__ A, c
         for (int q = 0; q < 4; ++q) {
             const int gk = k0 + lk + q;
             if (lrow < BM) As[lk + q][lrow] = (srow >= 0 && gk < K) ? to_float(A[(size_t)srow * K + gk]) : 0.f;
-            Ws[lk + q][lrow] = (gn < N && gk < K) ? to_float(W[(size_t)gn * K + gk]) : 0.f;
+            Ws[lk + q][lrow] = (gn < N && gk < K) ? to_float(W[(size_t)gn * ldw + gk]) : 0.f;
         }
         __syncthreads();
 #pragma unroll
@@ -228,27 +257,116 @@ __global__ void moe_combine_kernel(const T* __restrict__ y, const int* __restric
     }
 }
 
+// out[r] = x[order[r] / top]: every (token, choice) pair's input row, in sorted order
+template <typename T>
+__global__ void moe_gather_kernel(const T* __restrict__ x, const int* __restrict__ order, T* __restrict__ out, int dim, int top) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const T* src = x + (size_t)(order[blockIdx.x] / top) * dim;
+    T* dst = out + (size_t)blockIdx.x * dim;
+    constexpr int VEC = Vec16<T>::N;
+    if (dim % VEC == 0 && (((size_t)x | (size_t)out) & 15u) == 0) {
+        for (int d = threadIdx.x * VEC; d < dim; d += blockDim.x * VEC) {
+            Vec16<T> v;
+            v.load(src + d);
+            v.store(dst + d);
+        }
+    } else {
+        for (int d = threadIdx.x; d < dim; d += blockDim.x) dst[d] = src[d];
+    }
+}
+
+// All experts' hidden rows of a few tokens at once: u is [splits][T][n_experts * hidden + extra] (the product of
+// the tokens with every expert's up matrix, stacked, and `extra` more columns of a shared expert); a column of
+// expert e leaves as act(u) * weight(t, e), zero where the token did not choose e, an extra column as
+// act(u) * gate[t] (or act(u)).
+template <typename TI, typename TO>
+__global__ void moe_scale_act_kernel(const TI* __restrict__ u, int splits, long long plane, const int* __restrict__ chosen,
+                                     const float* __restrict__ weights, const float* __restrict__ gate, TO* __restrict__ out,
+                                     int n_experts, int hidden, int extra, int top, int act) {
+    extern __shared__ float wexp[];      // [n_experts]: this token's weight per expert
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const int t = blockIdx.x, width = n_experts * hidden + extra;
+    for (int e = threadIdx.x; e < n_experts; e += blockDim.x) wexp[e] = 0.f;
+    __syncthreads();
+    if (threadIdx.x < top) wexp[chosen[(size_t)t * top + threadIdx.x]] = weights[(size_t)t * top + threadIdx.x];
+    __syncthreads();
+    const float g = gate != nullptr ? gate[t] : 1.f;
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < width; c += gridDim.y * blockDim.x) {
+        const float w = c < n_experts * hidden ? wexp[c / hidden] : g;
+        float v = 0.f;
+        if (w != 0.f) {
+            for (int sp = 0; sp < splits; ++sp) v += to_float(u[(size_t)sp * plane + (size_t)t * width + c]);
+            v = act_apply(v, act) * w;
+        }
+        out[(size_t)t * width + c] = from_float<TO>(v);
+    }
+}
+
 }  // namespace
 
-// x: [n_tokens][dim] of dtype; w_router: float32 [n_rows][dim], n_rows = n_experts (+ 1 with gate != null);
+// out[r] = x[order[r] / top] for the n_pairs sorted rows; x: [n_tokens][dim]
+extern "C" int tl_moe_gather(const void* x, int dtype, const int* order, void* out, int n_pairs, int dim, int top, void* stream) {
+    if (n_pairs <= 0) return TL_OK;
+    if (dim <= 0 || top <= 0) return TL_BAD_SIZE;
+    const dim3 grid(n_pairs), block(dim >= 2048 ? 256 : 128);
+    if (dtype == TL_F32) return (int)tl_launch(moe_gather_kernel<float>, grid, block, 0, (cudaStream_t)stream, (const float*)x, order, (float*)out, dim, top);
+    if (dtype == TL_BF16) return (int)tl_launch(moe_gather_kernel<__nv_bfloat16>, grid, block, 0, (cudaStream_t)stream, (const __nv_bfloat16*)x, order, (__nv_bfloat16*)out, dim, top);
+    return TL_BAD_DTYPE;
+}
+
+// u: [splits][n_tokens][n_experts * hidden + extra] of in_dtype; out: the same row shape in out_dtype
+extern "C" int tl_moe_scale_act(const void* u, int in_dtype, int splits, long long plane, const int* chosen, const float* weights,
+                                const float* gate, void* out, int out_dtype, int n_tokens, int n_experts, int hidden, int extra,
+                                int top, int act, void* stream) {
+    if (n_tokens <= 0) return TL_OK;
+    if (n_experts <= 0 || hidden <= 0 || extra < 0 || top <= 0 || top > 1024 || splits < 1 || act < -1 || act > 2) return TL_BAD_SIZE;
+    const size_t smem = (size_t)n_experts * sizeof(float);
+    if (smem > 48 * 1024) return TL_TOO_LARGE;
+    const int width = n_experts * hidden + extra;
+    int by = (width + 256 * 8 - 1) / (256 * 8);
+    if (by < 1) by = 1;
+    const dim3 grid(n_tokens, by), block(256);
+    cudaStream_t s = (cudaStream_t)stream;
+#define TL_MOE_SA(TI, TO)                                                                                             \
+    tl_launch(moe_scale_act_kernel<TI, TO>, grid, block, smem, s, (const TI*)u, splits, plane, chosen, weights, gate, (TO*)out, \
+              n_experts, hidden, extra, top, act)
+    if (in_dtype == TL_F32 && out_dtype == TL_F32) return (int)TL_MOE_SA(float, float);
+    if (in_dtype == TL_F32 && out_dtype == TL_BF16) return (int)TL_MOE_SA(float, __nv_bfloat16);
+    if (in_dtype == TL_BF16 && out_dtype == TL_BF16) return (int)TL_MOE_SA(__nv_bfloat16, __nv_bfloat16);
+#undef TL_MOE_SA
+    return TL_BAD_DTYPE;
+}
+
+// Router logits of few tokens: x [n_tokens][dim] of dtype against w_router float32 [n_rows][dim], float32 out.
+// (Many tokens take the float32 product of gemm_simt instead, which reads the router once per 64 tokens.)
+extern "C" int tl_moe_logits(const void* x, int dtype, const float* w_router, float* logits, int n_tokens, int dim, int n_rows,
+                             void* stream) {
+    if (n_tokens <= 0 || n_rows <= 0) return TL_OK;
+    if (dim <= 0) return TL_BAD_SIZE;
+    const size_t smem = (size_t)dim * sizeof(float);
+    if (smem > 48 * 1024) return TL_TOO_LARGE;
+    const dim3 grid(n_tokens, (n_rows + 7) / 8), block(256);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == TL_F32) return (int)tl_launch(moe_logits_kernel<float>, grid, block, smem, s, (const float*)x, w_router, logits, dim, n_rows);
+    if (dtype == TL_BF16)
+        return (int)tl_launch(moe_logits_kernel<__nv_bfloat16>, grid, block, smem, s, (const __nv_bfloat16*)x, w_router, logits, dim, n_rows);
+    return TL_BAD_DTYPE;
+}
+
+// logits: float32 [n_tokens][n_rows], n_rows = n_experts (+ 1 with gate != null: the shared expert's gate);
 // correction: float32 [n_experts] or null; chosen: int32 [n_tokens][top]; weights: float32 [n_tokens][top];
 // gate: float32 [n_tokens] or null.
-extern "C" int tl_moe_route(const void* x, int dtype, const float* w_router, const float* correction, int* chosen,
-                            float* weights, float* gate, int n_tokens, int dim, int n_experts, int top, float scale,
-                            int renormalize, void* stream) {
+extern "C" int tl_moe_select(const float* logits, const float* correction, int* chosen, float* weights, float* gate,
+                             int n_tokens, int n_experts, int top, float scale, int renormalize, void* stream) {
     if (n_tokens <= 0) return TL_OK;
-    if (dim <= 0 || n_experts <= 0 || top <= 0 || top > n_experts) return TL_BAD_SIZE;
+    if (n_experts <= 0 || top <= 0 || top > n_experts) return TL_BAD_SIZE;
     const int n_rows = n_experts + (gate != nullptr ? 1 : 0);
-    const size_t smem = (size_t)(dim + n_rows + n_experts) * sizeof(float);
+    const size_t smem = (size_t)4 * 2 * n_experts * sizeof(float);
     if (smem > 48 * 1024) return TL_TOO_LARGE;
-    cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == TL_F32)
-        return (int)tl_launch(moe_route_kernel<float>, dim3(n_tokens), dim3(128), smem, s, (const float*)x, w_router, correction,
-                              chosen, weights, gate, dim, n_experts, n_rows, top, scale, renormalize);
-    if (dtype == TL_BF16)
-        return (int)tl_launch(moe_route_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(128), smem, s, (const __nv_bfloat16*)x, w_router,
-                              correction, chosen, weights, gate, dim, n_experts, n_rows, top, scale, renormalize);
-    return TL_BAD_DTYPE;
+    return (int)tl_launch(moe_select_kernel, dim3((n_tokens + 3) / 4), dim3(128), smem, (cudaStream_t)stream, logits, correction,
+                          chosen, weights, gate, n_tokens, n_experts, n_rows, top, scale, renormalize);
 }
 
 // rows of a tile for this many (token, choice) pairs, and how many tiles there can be at most
@@ -261,19 +379,23 @@ extern "C" int tl_moe_max_tiles(int n_pairs, int n_experts) {
 
 // chosen: int32 [n_pairs]; order, place: int32 [n_pairs]; tiles: int32 [1 + 3 * max_tiles] (count, then
 // expert, first row, rows of every tile)
-extern "C" int tl_moe_plan(const int* chosen, int n_pairs, int n_experts, int* order, int* place, int* tiles, void* stream) {
+// ends: int32 [n_experts] or null: where every expert's rows end in the sorted order
+extern "C" int tl_moe_plan(const int* chosen, int n_pairs, int n_experts, int* order, int* place, int* tiles, int* ends,
+                           void* stream) {
     if (n_pairs <= 0) return TL_OK;
     if (n_experts <= 0 || n_experts > 4096) return TL_BAD_SIZE;
     const size_t smem = (size_t)(2 * n_experts + 1) * sizeof(int);
     return (int)tl_launch(moe_plan_kernel, dim3(1), dim3(1024), smem, (cudaStream_t)stream, chosen, n_pairs, n_experts,
-                          tl_moe_tile_rows(n_pairs), order, place, tiles, tl_moe_max_tiles(n_pairs, n_experts));
+                          tl_moe_tile_rows(n_pairs), order, place, tiles, tl_moe_max_tiles(n_pairs, n_experts), ends);
 }
 
 // The experts' products over the sorted rows.  A: [rows][K]; with gather_div > 0 row r of the sorted order
-// reads A[order[r] / gather_div] (a token's row for each of its choices), else A[r].  W: [n_experts][N][K];
+// reads A[order[r] / gather_div] (a token's row for each of its choices), else A[r].  W: expert e's [N][K]
+// matrix starts w_expert elements after expert e - 1's and its rows lie ldw elements apart;
 // C: [n_pairs][N] in sorted order.  act: -1 none, 0 silu, 1 gelu (tanh form), 2 squared relu.
 extern "C" int tl_moe_gemm(const void* A, const void* W, void* C, int dtype, const int* tiles, const int* order,
-                           int gather_div, int n_pairs, int n_experts, int N, int K, int act, void* stream) {
+                           int gather_div, int n_pairs, int n_experts, int N, int K, int act, long long w_expert,
+                           long long ldw, void* stream) {
     if (n_pairs <= 0 || N <= 0) return TL_OK;
     if (K <= 0 || act < -1 || act > 2) return TL_BAD_SIZE;
     const int max_tiles = tl_moe_max_tiles(n_pairs, n_experts);
@@ -282,7 +404,7 @@ extern "C" int tl_moe_gemm(const void* A, const void* W, void* C, int dtype, con
     cudaStream_t s = (cudaStream_t)stream;
     const bool small = tl_moe_tile_rows(n_pairs) == 16;
 #define TL_MOE_GEMM(T, BM) \
-    tl_launch(moe_gemm_kernel<T, T, BM>, grid, block, 0, s, (const T*)A, (const T*)W, (T*)C, tiles, order, gather_div, N, K, act)
+    tl_launch(moe_gemm_kernel<T, T, BM>, grid, block, 0, s, (const T*)A, (const T*)W, (T*)C, tiles, order, gather_div, N, K, act, w_expert, ldw)
     if (dtype == TL_F32) return (int)(small ? TL_MOE_GEMM(float, 16) : TL_MOE_GEMM(float, 64));
     if (dtype == TL_BF16) return (int)(small ? TL_MOE_GEMM(__nv_bfloat16, 16) : TL_MOE_GEMM(__nv_bfloat16, 64));
 #undef TL_MOE_GEMM

@@ -494,8 +494,35 @@ class NativeOps:
         return self._act(gate_up, activation, out_dtype, True)
 
     def linear_gated_act(self, x: torch.Tensor, w_gate_up: torch.Tensor, *, activation: str) -> torch.Tensor:
-        """The gate/up product over the stacked weight ``[2 H, K]`` and ``act(gate) * up``, in ``x``'s dtype."""
+        """The gate/up product over the stacked weight ``[2 H, K]`` and ``act(gate) * up``, in ``x``'s dtype.
+        Decode-sized bfloat16 inputs whose product needs no K split run as one kernel (the gate in the
+        product's epilogue, as :meth:`linear_swiglu` does), everything else as product + gate kernel."""
+        if activation == "silu":
+            return self.linear_swiglu(x, w_gate_up)
+        _cuda_contig(x, "linear input")
+        _cuda_contig(w_gate_up, "linear weight")
+        _need(x.dim() == 2 and w_gate_up.dim() == 2 and x.shape[1] == w_gate_up.shape[1] and w_gate_up.shape[0] % 2 == 0,
+              "linear_gated_act: x [M, K] against w [2 H, K]")
+        M, K = x.shape
+        hidden = w_gate_up.shape[0] // 2
+        if (activation == "gelu_tanh" and x.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16 and self.use_tcgen05
+                and self.use_gated and M <= 64 and hidden % 64 == 0 and K % 8 == 0 and K >= 8 and x.data_ptr() % 16 == 0
+                and w_gate_up.data_ptr() % 16 == 0
+                and self._lib("gemm_tcgen05").tl_gemm_tcgen05_gated_supports(M, hidden, K) == 1):
+            return self.gemm_gated_gelu(x, w_gate_up)
         return self.gated_act(self.linear(x, w_gate_up, partials_ok=True), activation, out_dtype=x.dtype)
+
+    @_timed
+    def gemm_gated_gelu(self, x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
+        """The one-kernel form of :meth:`linear_gated_act` for ``gelu_tanh`` (its caller has checked the sizes)."""
+        M, K = x.shape
+        hidden = w_gate_up.shape[0] // 2
+        out = torch.empty((M, hidden), dtype=torch.bfloat16, device=x.device)
+        rc = self._lib("gemm_tcgen05").tl_gemm_tcgen05_gated_gelu(_ptr(x), _ptr(w_gate_up), _ptr(out), M, hidden, K,
+                                                                 ctypes.c_void_p(self._status.data_ptr()), _stream())
+        _check(rc, "gemm_tcgen05_gated_gelu")
+        self.launches += 1
+        return out
 
     @_timed
     def differential_combine(self, maps: torch.Tensor, lam: float, *, eps: float, out_scale: float,
@@ -596,7 +623,7 @@ class NativeOps:
                                 _ptr(bias), _ptr(state), _ptr(q_start), _ptr(state_slot), _ptr(fresh), _ptr(out), _DT[out_dtype],
                                 T, n_seqs, W, max_q_len, _ptr(ws), _stream())
         _check(rc, "mingru_scan")
-        self.launches += 2 if max_q_len > 64 else 1
+        self.launches += 3 if max_q_len > 16 else 1
         return out
 
     # ----------------------------------------------------------------- experts
@@ -614,16 +641,32 @@ class NativeOps:
         if correction is not None:
             _cuda_contig(correction, "correction", torch.float32)
             _need(correction.numel() == n_experts, "one correction per expert")
-        T = x.shape[0]
+        T, dim = x.shape
+        rows = w_router.shape[0]
+        lib = self._lib("moe")
+        if T <= 64:
+            # few tokens: a warp per (token, router row)
+            logits = torch.empty((T, rows), dtype=torch.float32, device=x.device)
+            _check(lib.tl_moe_logits(_ptr(x), _DT[x.dtype], _ptr(w_router), _ptr(logits), T, dim, rows, _stream()), "moe_logits")
+            self.launches += 1
+        elif x.dtype == torch.float32:
+            logits = self.gemm_simt(x, w_router, torch.float32)
+        else:
+            # many tokens: the float32 product (the rows as the rounded stream holds them, the arithmetic in 32-bit)
+            logits = torch.empty((T, rows), dtype=torch.float32, device=x.device)
+            _check(self._lib("gemm_simt").tl_gemm_simt_rows_bf16(_ptr(x), _ptr(w_router), _ptr(logits), T, rows, dim, _stream()),
+                   "gemm_simt (router)")
+            self.launches += 1
         chosen = torch.empty((T, top), dtype=torch.int32, device=x.device)
         weights = torch.empty((T, top), dtype=torch.float32, device=x.device)
         gate = torch.empty((T,), dtype=torch.float32, device=x.device) if shared_gate else None
-        rc = self._lib("moe").tl_moe_route(_ptr(x), _DT[x.dtype], _ptr(w_router), _ptr(correction), _ptr(chosen), _ptr(weights),
-                                          _ptr(gate), T, x.shape[1], n_experts, top, ctypes.c_float(scale),
-                                          1 if renormalize else 0, _stream())
-        _check(rc, "moe_route")
+        rc = lib.tl_moe_select(_ptr(logits), _ptr(correction), _ptr(chosen), _ptr(weights), _ptr(gate), T, n_experts, top,
+                               ctypes.c_float(scale), 1 if renormalize else 0, _stream())
+        _check(rc, "moe_select")
         self.launches += 1
         return chosen, weights, gate
+
+    GROUPED_MIN_PAIRS = 257      # (token, choice) pairs from which the experts' products of bfloat16 go to the library
 
     @_timed
     def moe_experts(self, x: torch.Tensor, chosen: torch.Tensor, weights: torch.Tensor, w_up: torch.Tensor,
@@ -631,8 +674,11 @@ class NativeOps:
                     shared_gate: Optional[torch.Tensor] = None) -> torch.Tensor:
         """``out[t] = sum_k weights[t, k] * down_e(act(up_e x[t]))`` with ``e = chosen[t, k]``, plus
         ``shared[t]`` (``[T, dim]`` or float32 partial sums) times ``shared_gate[t]`` where given.
-        ``w_up`` is ``[E, hidden, dim]``, ``w_down`` ``[E, dim, hidden]``.  The (token, choice) pairs are
-        sorted by expert on the device and both products run grouped over the sorted rows."""
+        ``w_up`` is ``[E, hidden, dim]``; ``w_down`` is ``[dim, >= E * hidden]``, expert ``e``'s matrix being
+        the columns ``e * hidden .. (e + 1) * hidden`` (the layout in which all experts are one
+        matrix too).  The (token, choice) pairs are sorted by expert on the device and both products
+        run grouped over the sorted rows: float32 multiply-adds of this library, or, for many rows of
+        bfloat16, the library's grouped product, as ``linear`` does for so many rows."""
         _cuda_contig(x, "experts' input")
         _cuda_contig(chosen, "chosen", torch.int32)
         _cuda_contig(weights, "weights", torch.float32)
@@ -644,19 +690,33 @@ class NativeOps:
         T, dim = x.shape
         top = chosen.shape[1]
         E, hidden = w_up.shape[0], w_up.shape[1]
-        _need(w_up.shape == (E, hidden, dim) and w_down.shape == (E, dim, hidden), "experts: w_up [E, hidden, dim], w_down [E, dim, hidden]")
+        _need(w_up.shape == (E, hidden, dim) and w_down.dim() == 2 and w_down.shape[0] == dim and w_down.shape[1] >= E * hidden,
+              "experts: w_up [E, hidden, dim], w_down [dim, >= E * hidden]")
+        ldd = w_down.shape[1]
         lib = self._lib("moe")
         pairs = T * top
         max_tiles = lib.tl_moe_max_tiles(pairs, E)
-        index = torch.empty(2 * pairs + 1 + 3 * max_tiles, dtype=torch.int32, device=x.device)
-        order, place, tiles = index[:pairs], index[pairs:2 * pairs], index[2 * pairs:]
-        _check(lib.tl_moe_plan(_ptr(chosen), pairs, E, _ptr(order), _ptr(place), _ptr(tiles), _stream()), "moe_plan")
-        u = torch.empty((pairs, hidden), dtype=x.dtype, device=x.device)
-        _check(lib.tl_moe_gemm(_ptr(x), _ptr(w_up), _ptr(u), _DT[x.dtype], _ptr(tiles), _ptr(order), top, pairs, E, hidden, dim,
-                               self._ACTS[activation], _stream()), "moe_gemm (up)")
-        y = torch.empty((pairs, dim), dtype=x.dtype, device=x.device)
-        _check(lib.tl_moe_gemm(_ptr(u), _ptr(w_down), _ptr(y), _DT[x.dtype], _ptr(tiles), _ptr(order), 0, pairs, E, dim, hidden,
-                               -1, _stream()), "moe_gemm (down)")
+        index = torch.empty(2 * pairs + E + 1 + 3 * max_tiles, dtype=torch.int32, device=x.device)
+        order, place, ends, tiles = index[:pairs], index[pairs:2 * pairs], index[2 * pairs:2 * pairs + E], index[2 * pairs + E:]
+        _check(lib.tl_moe_plan(_ptr(chosen), pairs, E, _ptr(order), _ptr(place), _ptr(tiles), _ptr(ends), _stream()), "moe_plan")
+        self.launches += 1
+        grouped = getattr(torch, "_grouped_mm", None)
+        if (x.dtype == torch.bfloat16 and pairs >= self.GROUPED_MIN_PAIRS and grouped is not None
+                and dim % 8 == 0 and hidden % 8 == 0 and ldd % 8 == 0):
+            xs = torch.empty((pairs, dim), dtype=x.dtype, device=x.device)
+            _check(lib.tl_moe_gather(_ptr(x), _DT[x.dtype], _ptr(order), _ptr(xs), pairs, dim, top, _stream()), "moe_gather")
+            self.launches += 1
+            u = self.activation(grouped(xs, w_up.transpose(1, 2), offs=ends, out_dtype=x.dtype), activation)
+            y = grouped(u, w_down.as_strided((E, hidden, dim), (hidden, 1, ldd)), offs=ends, out_dtype=x.dtype)
+        else:
+            u = torch.empty((pairs, hidden), dtype=x.dtype, device=x.device)
+            _check(lib.tl_moe_gemm(_ptr(x), _ptr(w_up), _ptr(u), _DT[x.dtype], _ptr(tiles), _ptr(order), top, pairs, E, hidden, dim,
+                                   self._ACTS[activation], ctypes.c_longlong(hidden * dim), ctypes.c_longlong(dim), _stream()),
+                   "moe_gemm (up)")
+            y = torch.empty((pairs, dim), dtype=x.dtype, device=x.device)
+            _check(lib.tl_moe_gemm(_ptr(u), _ptr(w_down), _ptr(y), _DT[x.dtype], _ptr(tiles), _ptr(order), 0, pairs, E, dim, hidden,
+                                   -1, ctypes.c_longlong(hidden), ctypes.c_longlong(ldd), _stream()), "moe_gemm (down)")
+            self.launches += 2
         splits, plane = 1, 0
         if shared is not None:
             _cuda_contig(shared, "shared expert's output")
@@ -673,7 +733,42 @@ class NativeOps:
                                 _DT[shared.dtype] if shared is not None else 0, splits, ctypes.c_longlong(plane), _ptr(shared_gate),
                                 _ptr(out), T, dim, top, _stream())
         _check(rc, "moe_combine")
-        self.launches += 4
+        self.launches += 1
+        return out
+
+    def moe_prefers_dense(self, n_tokens: int, top: int, n_experts: int, dtype: torch.dtype) -> bool:
+        """Whether a step of so many tokens should take all experts as one matrix (:meth:`moe_dense_hidden`):
+        few tokens in bfloat16 that between them touch a good part of the experts anyway.  The weights
+        are then read once, at the speed of the decode products, and the rows of experts that a token
+        did not choose are multiplied by zero."""
+        return dtype == torch.bfloat16 and self.use_tcgen05 and n_tokens <= 64 and 3 * n_tokens * top >= n_experts
+
+    @_timed
+    def moe_dense_hidden(self, x: torch.Tensor, chosen: torch.Tensor, weights: torch.Tensor, gate: Optional[torch.Tensor],
+                         w_up_all: torch.Tensor, *, n_experts: int, hidden: int, activation: str) -> torch.Tensor:
+        """The hidden rows of *all* experts for a few tokens: ``w_up_all`` is every expert's up matrix
+        stacked (``[E * hidden + extra, dim]``, the ``extra`` rows a shared expert's); returns
+        ``[T, E * hidden + extra]`` with ``act(up_e x[t]) * weight(t, e)`` in expert ``e``'s columns (zero
+        where the token did not choose it) and ``act(.) * gate[t]`` in the extra ones.  The product of
+        that with the experts' down matrices side by side (``[dim, E * hidden + extra]``) is the layer's
+        output."""
+        _cuda_contig(chosen, "chosen", torch.int32)
+        _cuda_contig(weights, "weights", torch.float32)
+        _need(activation in self._ACTS, f"unknown activation {activation!r}")
+        T, top = chosen.shape
+        width = w_up_all.shape[0]
+        extra = width - n_experts * hidden
+        _need(extra >= 0 and x.shape[0] == T and weights.shape == chosen.shape, "moe_dense_hidden: shapes disagree")
+        if gate is not None:
+            _cuda_contig(gate, "shared gate", torch.float32)
+        u = self.linear(x, w_up_all, partials_ok=True)
+        splits = u.shape[0] if u.dim() == 3 else 1
+        out = torch.empty((T, width), dtype=x.dtype, device=x.device)
+        rc = self._lib("moe").tl_moe_scale_act(_ptr(u), _DT[u.dtype], splits, ctypes.c_longlong(u.stride(0) if splits > 1 else 0),
+                                              _ptr(chosen), _ptr(weights), _ptr(gate), _ptr(out), _DT[x.dtype], T, n_experts, hidden,
+                                              extra, top, self._ACTS[activation], _stream())
+        _check(rc, "moe_scale_act")
+        self.launches += 1
         return out
 
     def can_fuse_residual(self, pending, h: torch.Tensor) -> bool:

@@ -2,8 +2,11 @@
 
 Routing runs on the device: a kernel takes the router's scores and picks the experts, another
 sorts the (token, expert) pairs by expert, the experts' products run as one grouped product over
-the sorted rows, and a last kernel adds up every token's weighted results.  Nothing is read back,
-so the shapes of a step's launches depend on its token count alone.
+the sorted rows, and a last kernel adds up every token's weighted results.  A step of few tokens
+that touch most experts between them (a decode batch) instead takes all experts as one matrix
+each way, with zeros where a token did not choose an expert: the weights stream once at the
+speed of the other decode products.  Nothing is read back, so the shapes of a step's launches
+depend on its token count alone.
 """
 
 from __future__ import annotations
@@ -12,6 +15,7 @@ from typing import Dict, Mapping, Optional
 
 import torch
 
+from ..kernels.lazy import PendingProduct
 from ..weights.loader import ExpectedTensor
 from .base import BuildEnv, FeedForward, as_compute, register_feed_forward
 
@@ -53,10 +57,14 @@ class RoutedExperts(FeedForward):
         self.shared_gate = bool(shared_gate)
         self.w_router: Optional[torch.Tensor] = None       # float32 [E (+ 1), dim]: the gate's row rides along
         self.correction: Optional[torch.Tensor] = None
-        self.w_up: Optional[torch.Tensor] = None           # [E, hidden, dim]
-        self.w_down: Optional[torch.Tensor] = None         # [E, dim, hidden]
-        self.w_shared_up: Optional[torch.Tensor] = None
-        self.w_shared_down: Optional[torch.Tensor] = None
+        # every expert's up matrix stacked, the shared expert's last: [E * hidden + shared, dim]; the down matrices
+        # side by side in the same order: [dim, E * hidden + shared].  The grouped products read an expert's own
+        # block of either; a step that touches most experts anyway takes each as one matrix.
+        self.w_up_all: Optional[torch.Tensor] = None
+        self.w_down_all: Optional[torch.Tensor] = None
+        self.w_up: Optional[torch.Tensor] = None           # [E, hidden, dim], a view of w_up_all
+        self.w_shared_up: Optional[torch.Tensor] = None    # a view of w_up_all
+        self.w_shared_down: Optional[torch.Tensor] = None  # a copy of its own (the products want whole rows)
 
     def expected_tensors(self) -> Dict[str, ExpectedTensor]:
         out = {"router.weight": ExpectedTensor((self.n_experts, self.dim))}
@@ -80,25 +88,38 @@ class RoutedExperts(FeedForward):
         self.w_router = torch.cat(rows).contiguous()
         if self.choice_correction:
             self.correction = tensors["correction"].to(**f32).contiguous()
-        self.w_up = torch.stack([as_compute(tensors[f"experts.{e}.up.weight"], self.env) for e in range(self.n_experts)])
-        self.w_down = torch.stack([as_compute(tensors[f"experts.{e}.down.weight"], self.env) for e in range(self.n_experts)])
+        ups = [as_compute(tensors[f"experts.{e}.up.weight"], self.env) for e in range(self.n_experts)]
+        downs = [as_compute(tensors[f"experts.{e}.down.weight"], self.env) for e in range(self.n_experts)]
         if self.shared_hidden:
-            self.w_shared_up = as_compute(tensors["shared.up.weight"], self.env)
-            self.w_shared_down = as_compute(tensors["shared.down.weight"], self.env)
+            ups.append(as_compute(tensors["shared.up.weight"], self.env))
+            downs.append(as_compute(tensors["shared.down.weight"], self.env))
+            self.w_shared_down = downs[-1]
+        self.w_up_all = torch.cat(ups).contiguous()
+        self.w_down_all = torch.cat(downs, dim=1).contiguous()
+        n = self.n_experts * self.hidden
+        self.w_up = self.w_up_all[:n].view(self.n_experts, self.hidden, self.dim)
+        if self.shared_hidden:
+            self.w_shared_up = self.w_up_all[n:]
 
     def weight_bytes(self) -> int:
-        """What a step reads at most: the router, the shared expert, and ``top`` experts per token
-        (a step of few tokens leaves most experts alone; this counts all of them)."""
-        return super().weight_bytes()
+        """What a step reads at most: the router and every expert (a step of few tokens leaves most
+        experts alone; this counts all of them)."""
+        return sum(t.numel() * t.element_size() for t in (self.w_router, self.w_up_all, self.w_down_all))
 
-    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, ctx):
         ops = self.env.ops
         chosen, weights, gate = ops.moe_route(x, self.w_router, self.correction, n_experts=self.n_experts, top=self.top,
                                               scale=self.router_scale, renormalize=self.renormalize,
                                               shared_gate=self.shared_gate)
+        if ops.moe_prefers_dense(x.shape[0], self.top, self.n_experts, x.dtype):
+            # few tokens that touch most experts between them: every expert (and the shared one) as one
+            # matrix each way, the rows of experts a token did not choose multiplied by zero
+            u = ops.moe_dense_hidden(x, chosen, weights, gate, self.w_up_all, n_experts=self.n_experts, hidden=self.hidden,
+                                     activation=self.activation)
+            return PendingProduct(u, self.w_down_all)
         shared = None
         if self.shared_hidden:
             u = ops.activation(ops.linear(x, self.w_shared_up, partials_ok=True), self.activation, out_dtype=self.env.dtype)
             shared = ops.linear(u, self.w_shared_down, partials_ok=True)
-        return ops.moe_experts(x, chosen, weights, self.w_up, self.w_down, activation=self.activation,
+        return ops.moe_experts(x, chosen, weights, self.w_up, self.w_down_all, activation=self.activation,
                                shared=shared, shared_gate=gate)
