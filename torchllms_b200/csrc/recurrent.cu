@@ -20,7 +20,7 @@
 
 namespace {
 
-constexpr int CHUNK = 16;     // tokens a thread walks in one go
+constexpr int CHUNK = 8;      // tokens a thread walks in one go
 constexpr int NT = 128;
 
 struct ScanParams {
@@ -46,18 +46,24 @@ __device__ __forceinline__ float column(const ScanParams& p, size_t at) {
     return x;
 }
 
-__device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + expf(-x)); }
+// FAST (results that leave as bfloat16): the hardware's exponential and reciprocal, good to a few units in the
+// last place of float32; the float32 mode takes the library's.
+template <bool FAST>
+__device__ __forceinline__ float sigmoidf_(float x) {
+    return FAST ? __fdividef(1.f, 1.f + __expf(-x)) : 1.f / (1.f + expf(-x));
+}
 
 // S <- keep * S + add from a token's z and u columns (biases added)
+template <bool FAST>
 __device__ __forceinline__ void token_terms(float z, float u, float& keep, float& add) {
-    const float a = sigmoidf_(z);
-    const float cand = u >= 0.f ? u + 0.5f : sigmoidf_(u);
+    const float a = sigmoidf_<FAST>(z);
+    const float cand = u >= 0.f ? u + 0.5f : sigmoidf_<FAST>(u);
     keep = 1.f - a;
     add = a * cand;
 }
 
-template <typename TI>
-__global__ void __launch_bounds__(NT) mingru_pairs_kernel(const ScanParams p) {
+template <typename TI, bool FAST>
+__global__ void __launch_bounds__(NT, 8) mingru_pairs_kernel(const ScanParams p) {
     grid_launch_dependents();
     grid_dependency_wait();
     const int c = blockIdx.x * NT + threadIdx.x;
@@ -69,16 +75,18 @@ __global__ void __launch_bounds__(NT) mingru_pairs_kernel(const ScanParams p) {
     float z[CHUNK], u[CHUNK];
 #pragma unroll
     for (int i = 0; i < CHUNK; ++i) {
-        const size_t row = (size_t)(t0 + (i < n ? i : 0)) * 3 * p.W;
-        z[i] = column<TI>(p, row + c) + bz;
-        u[i] = column<TI>(p, row + p.W + c) + bu;
+        if (i < n) {
+            const size_t row = (size_t)(t0 + i) * 3 * p.W;
+            z[i] = column<TI>(p, row + c) + bz;
+            u[i] = column<TI>(p, row + p.W + c) + bu;
+        }
     }
     float P = 1.f, R = 0.f;
 #pragma unroll
     for (int i = 0; i < CHUNK; ++i) {
         if (i < n) {
             float keep, add;
-            token_terms(z[i], u[i], keep, add);
+            token_terms<FAST>(z[i], u[i], keep, add);
             P *= keep;
             R = fmaf(keep, R, add);
         }
@@ -121,8 +129,8 @@ __global__ void __launch_bounds__(NT) mingru_starts_kernel(const ScanParams p) {
     if (chunks > 0) *st = S;
 }
 
-template <typename TI, typename TO>
-__global__ void __launch_bounds__(NT) mingru_scan_kernel(const ScanParams p) {
+template <typename TI, typename TO, bool FAST>
+__global__ void __launch_bounds__(NT, 8) mingru_scan_kernel(const ScanParams p) {
     grid_launch_dependents();
     grid_dependency_wait();
     const int c = blockIdx.x * NT + threadIdx.x;
@@ -134,10 +142,12 @@ __global__ void __launch_bounds__(NT) mingru_scan_kernel(const ScanParams p) {
     float z[CHUNK], u[CHUNK], g[CHUNK];
 #pragma unroll
     for (int i = 0; i < CHUNK; ++i) {
-        const size_t row = (size_t)(t0 + (i < n ? i : 0)) * 3 * p.W;
-        z[i] = column<TI>(p, row + c) + bz;
-        u[i] = column<TI>(p, row + p.W + c) + bu;
-        g[i] = column<TI>(p, row + 2 * p.W + c) + bg;
+        if (i < n) {
+            const size_t row = (size_t)(t0 + i) * 3 * p.W;
+            z[i] = column<TI>(p, row + c) + bz;
+            u[i] = column<TI>(p, row + p.W + c) + bu;
+            g[i] = column<TI>(p, row + 2 * p.W + c) + bg;
+        }
     }
     float* st = p.state + (size_t)p.state_slot[b] * p.W + c;
     float S = p.n_chunks == 1 ? (p.fresh[b] ? 0.f : *st) : p.starts[((size_t)b * p.n_chunks + chunk) * p.W + c];
@@ -146,9 +156,9 @@ __global__ void __launch_bounds__(NT) mingru_scan_kernel(const ScanParams p) {
     for (int i = 0; i < CHUNK; ++i) {
         if (i < n) {
             float keep, add;
-            token_terms(z[i], u[i], keep, add);
+            token_terms<FAST>(z[i], u[i], keep, add);
             S = fmaf(keep, S, add);
-            out[(size_t)(t0 + i) * p.W + c] = from_float<TO>(S * g[i] * sigmoidf_(g[i]));
+            out[(size_t)(t0 + i) * p.W + c] = from_float<TO>(S * g[i] * sigmoidf_<FAST>(g[i]));
         }
     }
     if (p.n_chunks == 1) *st = S;     // (longer portions: the walk over the chunks left the state)
@@ -181,17 +191,17 @@ extern "C" int tl_mingru_scan(const void* proj, int in_dtype, int splits, long l
     cudaStream_t s = (cudaStream_t)stream;
     const dim3 grid((width + NT - 1) / NT, p.n_chunks, n_seqs), block(NT);
     cudaError_t e = cudaSuccess;
-#define TL_SCAN(TI, TO)                                                                          \
+#define TL_SCAN(TI, TO, FAST)                                                                          \
     do {                                                                                         \
         if (p.n_chunks > 1) {                                                                    \
-            e = tl_launch(mingru_pairs_kernel<TI>, grid, block, 0, s, p);                        \
+            e = tl_launch(mingru_pairs_kernel<TI, FAST>, grid, block, 0, s, p);                  \
             if (e == cudaSuccess) e = tl_launch(mingru_starts_kernel, dim3(grid.x, 1, n_seqs), block, 0, s, p); \
         }                                                                                        \
-        if (e == cudaSuccess) e = tl_launch(mingru_scan_kernel<TI, TO>, grid, block, 0, s, p);   \
+        if (e == cudaSuccess) e = tl_launch(mingru_scan_kernel<TI, TO, FAST>, grid, block, 0, s, p); \
     } while (0)
-    if (in_dtype == TL_F32 && out_dtype == TL_F32) TL_SCAN(float, float);
-    else if (in_dtype == TL_F32 && out_dtype == TL_BF16) TL_SCAN(float, __nv_bfloat16);
-    else if (in_dtype == TL_BF16 && out_dtype == TL_BF16) TL_SCAN(__nv_bfloat16, __nv_bfloat16);
+    if (in_dtype == TL_F32 && out_dtype == TL_F32) TL_SCAN(float, float, false);
+    else if (in_dtype == TL_F32 && out_dtype == TL_BF16) TL_SCAN(float, __nv_bfloat16, true);
+    else if (in_dtype == TL_BF16 && out_dtype == TL_BF16) TL_SCAN(__nv_bfloat16, __nv_bfloat16, true);
     else return TL_BAD_DTYPE;
 #undef TL_SCAN
     return (int)e;

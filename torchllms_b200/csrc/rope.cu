@@ -274,7 +274,8 @@ __global__ void rope_store_kernel(const TI* __restrict__ proj, int splits, long 
     };
     // a head's work items: `half` rotated pairs, then the coordinates that pass
     const int per_head = head_dim - half;
-    for (int w = threadIdx.x; w < qk_heads * per_head; w += blockDim.x) {
+    const int first = blockIdx.y * blockDim.x + threadIdx.x, step = gridDim.y * blockDim.x;    // a token's work may be spread over CTAs
+    for (int w = first; w < qk_heads * per_head; w += step) {
         const int head = w / per_head, i = w - head * per_head;
         if (i < half) {
             const int l0 = interleaved ? 2 * i : i, l1 = interleaved ? 2 * i + 1 : i + half;
@@ -288,12 +289,12 @@ __global__ void rope_store_kernel(const TI* __restrict__ proj, int splits, long 
         }
     }
     if (write && v_pages != nullptr) {
-        for (int c = threadIdx.x; c < n_v; c += blockDim.x) {
+        for (int c = first; c < n_v; c += step) {
             const int head = c / v_head_dim, d = c - head * v_head_dim;
             v_pages[(((size_t)page * n_v_heads + head) * page_size + slot) * v_head_dim + d] = from_float<T>(value(n_qk + c));
         }
     }
-    for (int c = threadIdx.x; c < n_extra; c += blockDim.x)
+    for (int c = first; c < n_extra; c += step)
         extra_out[(size_t)t * n_extra + c] = from_float<T>(1.f / (1.f + expf(-value(n_qk + n_v + c))));
 }
 
@@ -314,9 +315,15 @@ extern "C" int tl_rope_store(const void* proj, int in_dtype, int splits, const i
     const long long width = (long long)(n_q_heads + n_k_heads) * head_dim + (long long)n_v_heads * v_head_dim + n_extra;
     const long long plane = (long long)n_tokens * width;
     const int threads = width >= 2048 ? 256 : 128;
+    // few tokens (decoding): a token's row is spread over several CTAs
+    int by = 1;
+    if (n_tokens < 256) {
+        by = (int)((width + 2 * threads - 1) / (2 * threads));
+        if (by > 16) by = 16;
+    }
     cudaStream_t s = (cudaStream_t)stream;
 #define TL_ROPE_STORE(TI, T)                                                                                          \
-    tl_launch(rope_store_kernel<TI, T>, dim3(n_tokens), dim3(threads), 0, s, (const TI*)proj, splits, plane, positions, \
+    tl_launch(rope_store_kernel<TI, T>, dim3(n_tokens, by), dim3(threads), 0, s, (const TI*)proj, splits, plane, positions, \
               table, slot_mapping, (T*)q_out, (T*)extra_out, (T*)k_pages, (T*)v_pages, n_q_heads, n_k_heads, n_v_heads, \
               head_dim, v_head_dim, rot_dims, n_extra, page_size, table_rows, interleaved)
     if (in_dtype == TL_F32 && dtype == TL_F32) return (int)TL_ROPE_STORE(float, float);

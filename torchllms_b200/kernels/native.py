@@ -623,7 +623,7 @@ class NativeOps:
                                 _ptr(bias), _ptr(state), _ptr(q_start), _ptr(state_slot), _ptr(fresh), _ptr(out), _DT[out_dtype],
                                 T, n_seqs, W, max_q_len, _ptr(ws), _stream())
         _check(rc, "mingru_scan")
-        self.launches += 3 if max_q_len > 16 else 1
+        self.launches += 3 if max_q_len > 8 else 1
         return out
 
     # ----------------------------------------------------------------- experts
@@ -651,12 +651,16 @@ class NativeOps:
             self.launches += 1
         elif x.dtype == torch.float32:
             logits = self.gemm_simt(x, w_router, torch.float32)
-        else:
-            # many tokens: the float32 product (the rows as the rounded stream holds them, the arithmetic in 32-bit)
+        elif torch.backends.cuda.matmul.allow_tf32:
+            # many tokens, and the library's float32 product would not be one: this library's own
             logits = torch.empty((T, rows), dtype=torch.float32, device=x.device)
             _check(self._lib("gemm_simt").tl_gemm_simt_rows_bf16(_ptr(x), _ptr(w_router), _ptr(logits), T, rows, dim, _stream()),
                    "gemm_simt (router)")
             self.launches += 1
+        else:
+            # many tokens: the library's float32 product of the rows as the rounded stream holds them (true
+            # 32-bit arithmetic: the reduced-precision matrix mode is off), as linear() takes the library for so many rows
+            logits = torch.mm(x.float(), w_router.t())
         chosen = torch.empty((T, top), dtype=torch.int32, device=x.device)
         weights = torch.empty((T, top), dtype=torch.float32, device=x.device)
         gate = torch.empty((T,), dtype=torch.float32, device=x.device) if shared_gate else None
