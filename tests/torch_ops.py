@@ -211,6 +211,44 @@ class TorchOps:
             cols = torch.cat([cols, (gate[:, None] if gate is not None else torch.ones(T, 1)).expand(T, extra)], dim=1)
         return (u * cols).to(x.dtype)
 
+    def glu(self, gate_up, out_dtype=None, *, limit, alpha, up_offset):
+        out_dtype = out_dtype or gate_up.dtype
+        if gate_up.dim() == 3:
+            gate_up = gate_up.float().sum(0)
+        hidden = gate_up.shape[1] // 2
+        g = gate_up[:, :hidden].float().clamp(max=limit)
+        u = gate_up[:, hidden:].float().clamp(min=-limit, max=limit)
+        return (g * torch.sigmoid(alpha * g) * (u + up_offset)).to(out_dtype)
+
+    def linear_glu(self, x, w_gate_up, *, limit, alpha, up_offset):
+        return self.glu(self.linear(x, w_gate_up, partials_ok=True), out_dtype=x.dtype, limit=limit, alpha=alpha,
+                        up_offset=up_offset)
+
+    def project_and_store(self, proj, *, n_q, n_k, n_v, n_extra, bias, q_norm, k_norm, eps, k_pages, v_pages,
+                          slot_mapping, page_size, out_dtype):
+        """A row of proj is [q | k | v | extra].  Bias added, q and k each normalised over their whole
+        width (where a weight is given), k and v written to their pages, sigmoid of the extra columns."""
+        x = proj.float().sum(0) if proj.dim() == 3 else proj.float()
+        assert x.shape[1] == n_q + n_k + n_v + n_extra
+        if bias is not None:
+            x = x + bias
+        q, k, v, e = x.split([n_q, n_k, n_v, n_extra], dim=1)
+        if q_norm is not None:
+            q = q * torch.rsqrt(q.pow(2).mean(-1, keepdim=True) + eps) * q_norm
+        if k_norm is not None and n_k:
+            k = k * torch.rsqrt(k.pow(2).mean(-1, keepdim=True) + eps) * k_norm
+        if k_pages is not None and n_k:
+            sm = slot_mapping.long()
+            page, slot = sm // page_size, sm % page_size
+            k_pages[page, :, slot] = k.reshape(k.shape[0], k_pages.shape[1], k_pages.shape[3]).to(k_pages.dtype)
+            if v_pages is not None and n_v:
+                v_pages[page, :, slot] = v.reshape(v.shape[0], v_pages.shape[1], v_pages.shape[3]).to(v_pages.dtype)
+        return q.to(out_dtype).contiguous(), (torch.sigmoid(e).to(out_dtype).contiguous() if n_extra else None)
+
+    def head_linear(self, x, w):
+        """x [T, H, K] against w [H, N, K]: out[t, h] = w[h] @ x[t, h]."""
+        return torch.einsum("thk,hnk->thn", x.float(), w.float()).to(x.dtype).contiguous()
+
     def rmsnorm(self, h, delta, weight, eps, out_dtype, rows=None, deferred=False):
         if isinstance(delta, PendingProduct):
             delta = delta.take(self)
