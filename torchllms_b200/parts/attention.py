@@ -266,7 +266,7 @@ class DifferentialAttention(Mixer):
         self.n_k = 2 * self.n_kv_heads * self.head_dim
         self.n_v = self.n_kv_heads * self.v_head_dim
         env.ops.check_attention_sizes(2 * self.n_heads, 2 * self.n_kv_heads, self.head_dim, env.dtype, v_head_dim=self.v_head_dim)
-        self.table = precise_rotary_table(max(self.rot_dims, 2), rot_base, rot_factor, env.max_positions).to(env.device)
+        self.table = precise_rotary_table(max(self.rot_dims, 2), rot_base, rot_factor, env.max_positions, env.device)
         self.lam = 0.0
         self.w_in: Optional[torch.Tensor] = None
         self.wo: Optional[torch.Tensor] = None

@@ -54,13 +54,24 @@ def rotary_table(freq: torch.Tensor, max_positions: int) -> torch.Tensor:
     return torch.stack([torch.cos(angles), torch.sin(angles)], dim=-1).contiguous()
 
 
-def precise_rotary_table(dims: int, theta: float, factor: float, max_positions: int) -> torch.Tensor:
+_precise_tables: dict = {}
+
+
+def precise_rotary_table(dims: int, theta: float, factor: float, max_positions: int, device="cpu") -> torch.Tensor:
     """``[max_positions, dims / 2, 2]`` float32 (cos, sin) of the angles ``p * theta^(-2i/dims) / factor``,
-    the angles taken in 64-bit so that the table is exact to float32 rounding at any position."""
-    i = torch.arange(dims // 2, dtype=torch.float64)
-    freq = float(theta) ** (-2.0 * i / dims) / float(factor)
-    angles = torch.arange(max_positions, dtype=torch.float64)[:, None] * freq[None, :]
-    return torch.stack([torch.cos(angles), torch.sin(angles)], dim=-1).to(torch.float32).contiguous()
+    the angles taken in 64-bit so that the table is exact to float32 rounding at any position.
+    Layers with the same numbers on the same device share one table."""
+    key = (int(dims), float(theta), float(factor), int(max_positions), str(device))
+    table = _precise_tables.get(key)
+    if table is None:
+        i = torch.arange(dims // 2, dtype=torch.float64)
+        freq = float(theta) ** (-2.0 * i / dims) / float(factor)
+        angles = torch.arange(max_positions, dtype=torch.float64)[:, None] * freq[None, :]
+        table = torch.stack([torch.cos(angles), torch.sin(angles)], dim=-1).to(torch.float32).contiguous().to(device)
+        if len(_precise_tables) >= 8:
+            _precise_tables.clear()
+        _precise_tables[key] = table
+    return table
 
 
 @register_position_encoding("rope")
