@@ -294,12 +294,12 @@ def _nagolix_config(z, vocab, max_len):
 def _rakuvik_config(z, vocab, max_len):
     from torchllms_b200.models.rakuvik import AttentionConfig, LayerConfig, MinGruConfig, MlpConfig, RakuvikConfig
     att = AttentionConfig(heads=z["heads"], kv_heads=z["kv_heads"], dim=z["map_dim"], vdim=z["head_dim"], scale=z["map_dim"] ** -0.5,
-                          diff=0.5, rot_dims=z["rot_dims"], rot_base=500000.0, rot_factor=8.0)
+                          diff=0.4, rot_dims=z["rot_dims"], rot_base=1000000.0, rot_factor=4.0)
     att2 = AttentionConfig(heads=z["heads"], kv_heads=z["kv_heads"], dim=z["map_dim"], vdim=z["head_dim"], scale=z["map_dim"] ** -0.5,
-                           diff=0.5, rot_dims=z["rot_dims"], rot_base=500000.0, rot_factor=8.0, kv_from=1)
+                           diff=0.4, rot_dims=z["rot_dims"], rot_base=1000000.0, rot_factor=4.0, kv_from=1)
     gru = MinGruConfig(width=z["gru_width"])
     dense = MlpConfig("dense", z["ff"])
-    moe = MlpConfig("moe", z["expert_ff"], experts=z["experts"], top=z["top"], router_scale=1.5, shared_ff=z["shared_ff"])
+    moe = MlpConfig("moe", z["expert_ff"], experts=z["experts"], top=z["top"], router_scale=2.0, shared_ff=z["shared_ff"])
     kinds = [(gru, dense), (att, moe), (gru, moe), (att2, moe)]
     if z["layers"] % 4:
         raise ValueError("the Rakuvik workload's layers come in fours")

@@ -41,7 +41,7 @@ def dense(ff=80):
     return {"ff": ff, "kind": "dense"}
 
 
-def moe(experts=6, top=2, ff=24, scale=1.5, shared=40):
+def moe(experts=6, top=2, ff=24, scale=1.3, shared=40):
     out = {"expert": {"ff": ff}, "kind": "moe", "router": {"experts": experts, "scale": scale, "top": top}}
     if shared:
         out["shared"] = {"ff": shared}
@@ -58,7 +58,7 @@ CASES = {
     # the first one's keys and values
     "mixed": (config([
         mingru_layer(width=48, mlp=dense(80)),
-        attention_layer(heads=4, kv_heads=2, dim=16, vdim=24, rot_dims=8, factor=4.0, mlp=moe(6, 2, 24, 1.5, 40)),
+        attention_layer(heads=4, kv_heads=2, dim=16, vdim=24, rot_dims=8, factor=4.0, mlp=moe(6, 2, 24, 1.3, 40)),
         mingru_layer(width=80, mlp=None),
         attention_layer(heads=4, kv_heads=2, dim=16, vdim=24, rot_dims=8, factor=4.0, diff=0.3, kv_from=1, mlp=moe(5, 3, 16, 0.7, 0)),
         mingru_layer(width=32, mlp=moe(4, 1, 40, 1.0, 24)),
@@ -73,9 +73,9 @@ CASES = {
     ], width=44, vocab=61, eps=1e-4), 4),
     # sizes the tensor-core kernels take, prompts longer than the scan's chunk
     "wide": (config([
-        attention_layer(heads=4, kv_heads=1, dim=64, vdim=128, rot_dims=32, base=500000.0, factor=8.0, mlp=moe(8, 3, 64, 1.5, 128)),
-        mingru_layer(width=320, mlp=dense(384)),
-        attention_layer(heads=4, kv_heads=1, dim=64, vdim=128, rot_dims=32, base=500000.0, factor=8.0, kv_from=0, mlp=dense(256)),
+        attention_layer(heads=4, kv_heads=1, dim=64, vdim=128, rot_dims=48, base=250000.0, factor=6.0, mlp=moe(8, 2, 96, 1.25, 160)),
+        mingru_layer(width=288, mlp=dense(384)),
+        attention_layer(heads=4, kv_heads=1, dim=64, vdim=128, rot_dims=48, base=250000.0, factor=6.0, kv_from=0, mlp=dense(192)),
     ], width=256, vocab=211), 16),
 }
 
