@@ -236,24 +236,70 @@ __global__ void __launch_bounds__(NT) moe_gemm_kernel(const T* __restrict__ A, c
     }
 }
 
-// One CTA per token.  y: [pairs][dim] in sorted order; shared: [splits][T][dim] or null.
-template <typename T, typename TS>
+// One CTA per token.  y: [pairs][dim] in sorted order; shared: [splits][T][dim] or null.  The token's places and
+// weights are fetched once; VEC: sixteen bytes of a row per thread and turn, four choices' loads in flight.
+constexpr int COMBINE_TOP = 64;
+template <typename T, typename TS, bool VEC>
 __global__ void moe_combine_kernel(const T* __restrict__ y, const int* __restrict__ place, const float* __restrict__ weights,
                                    const TS* __restrict__ shared, int shared_splits, long long shared_plane,
                                    const float* __restrict__ gate, T* __restrict__ out, int dim, int top) {
+    __shared__ int pl[COMBINE_TOP];
+    __shared__ float wt[COMBINE_TOP];
     grid_launch_dependents();
     grid_dependency_wait();
     const int t = blockIdx.x;
-    for (int d = threadIdx.x; d < dim; d += blockDim.x) {
-        float acc = 0.f;
-        for (int k = 0; k < top; ++k)
-            acc = fmaf(weights[(size_t)t * top + k], to_float(y[(size_t)place[(size_t)t * top + k] * dim + d]), acc);
-        if (shared != nullptr) {
-            float sh = 0.f;
-            for (int s = 0; s < shared_splits; ++s) sh += to_float(shared[(size_t)s * shared_plane + (size_t)t * dim + d]);
-            acc = gate != nullptr ? fmaf(gate[t], sh, acc) : acc + sh;
+    if (threadIdx.x < top) {
+        pl[threadIdx.x] = place[(size_t)t * top + threadIdx.x];
+        wt[threadIdx.x] = weights[(size_t)t * top + threadIdx.x];
+    }
+    __syncthreads();
+    const float g = gate != nullptr ? gate[t] : 1.f;
+    if (VEC) {
+        constexpr int N = Vec16<T>::N;
+        for (int d = threadIdx.x * N; d < dim; d += blockDim.x * N) {
+            float acc[N];
+#pragma unroll
+            for (int e = 0; e < N; ++e) acc[e] = 0.f;
+            int k = 0;
+            for (; k + 4 <= top; k += 4) {
+                Vec16<T> v[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) v[i].load(y + (size_t)pl[k + i] * dim + d);
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+#pragma unroll
+                    for (int e = 0; e < N; ++e) acc[e] = fmaf(wt[k + i], v[i].get(e), acc[e]);
+            }
+            for (; k < top; ++k) {
+                Vec16<T> v;
+                v.load(y + (size_t)pl[k] * dim + d);
+#pragma unroll
+                for (int e = 0; e < N; ++e) acc[e] = fmaf(wt[k], v.get(e), acc[e]);
+            }
+            if (shared != nullptr) {
+#pragma unroll
+                for (int e = 0; e < N; ++e) {
+                    float sh = 0.f;
+                    for (int sp = 0; sp < shared_splits; ++sp) sh += to_float(shared[(size_t)sp * shared_plane + (size_t)t * dim + d + e]);
+                    acc[e] = fmaf(g, sh, acc[e]);
+                }
+            }
+            Vec16<T> o;
+#pragma unroll
+            for (int e = 0; e < N; ++e) o.set(e, acc[e]);
+            o.store(out + (size_t)t * dim + d);
         }
-        out[(size_t)t * dim + d] = from_float<T>(acc);
+    } else {
+        for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+            float acc = 0.f;
+            for (int k = 0; k < top; ++k) acc = fmaf(wt[k], to_float(y[(size_t)pl[k] * dim + d]), acc);
+            if (shared != nullptr) {
+                float sh = 0.f;
+                for (int s = 0; s < shared_splits; ++s) sh += to_float(shared[(size_t)s * shared_plane + (size_t)t * dim + d]);
+                acc = fmaf(g, sh, acc);
+            }
+            out[(size_t)t * dim + d] = from_float<T>(acc);
+        }
     }
 }
 
@@ -417,12 +463,18 @@ extern "C" int tl_moe_combine(const void* y, int dtype, const int* place, const 
                               int shared_dtype, int shared_splits, long long shared_plane, const float* gate, void* out,
                               int n_tokens, int dim, int top, void* stream) {
     if (n_tokens <= 0) return TL_OK;
-    if (dim <= 0 || top <= 0) return TL_BAD_SIZE;
-    const dim3 grid(n_tokens), block(dim >= 1024 ? 256 : 128);
+    if (dim <= 0 || top <= 0 || top > COMBINE_TOP) return TL_BAD_SIZE;
+    const int n16 = dtype == TL_F32 ? 4 : 8;          // elements in sixteen bytes
+    const bool vec = dim % n16 == 0 && aligned16(y) && aligned16(out);
+    int threads = vec ? ((dim / n16 + 31) / 32) * 32 : (dim >= 1024 ? 256 : 128);
+    threads = threads < 64 ? 64 : (threads > 256 ? 256 : threads);
+    const dim3 grid(n_tokens), block(threads);
     cudaStream_t s = (cudaStream_t)stream;
-#define TL_MOE_COMBINE(T, TS)                                                                                       \
-    tl_launch(moe_combine_kernel<T, TS>, grid, block, 0, s, (const T*)y, place, weights, (const TS*)shared, shared_splits, \
-              shared_plane, gate, (T*)out, dim, top)
+#define TL_MOE_COMBINE(T, TS)                                                                                          \
+    (vec ? tl_launch(moe_combine_kernel<T, TS, true>, grid, block, 0, s, (const T*)y, place, weights, (const TS*)shared,   \
+                     shared_splits, shared_plane, gate, (T*)out, dim, top)                                             \
+         : tl_launch(moe_combine_kernel<T, TS, false>, grid, block, 0, s, (const T*)y, place, weights, (const TS*)shared,  \
+                     shared_splits, shared_plane, gate, (T*)out, dim, top))
     if (dtype == TL_F32 && (shared == nullptr || shared_dtype == TL_F32)) return (int)TL_MOE_COMBINE(float, float);
     if (dtype == TL_BF16 && (shared == nullptr || shared_dtype == TL_BF16)) return (int)TL_MOE_COMBINE(__nv_bfloat16, __nv_bfloat16);
     if (dtype == TL_BF16 && shared_dtype == TL_F32) return (int)TL_MOE_COMBINE(__nv_bfloat16, float);

@@ -73,12 +73,29 @@ __global__ void __launch_bounds__(NT, 8) mingru_pairs_kernel(const ScanParams p)
     if (n <= 0) return;
     const float bz = p.bias ? p.bias[c] : 0.f, bu = p.bias ? p.bias[p.W + c] : 0.f;
     float z[CHUNK], u[CHUNK];
+    if (p.splits == 1) {
+        // one plane (prompt portions): every load is issued before anything waits for one; a short last chunk
+        // fetches its last token again in place of the absent ones
+        const TI* src = reinterpret_cast<const TI*>(p.proj);
 #pragma unroll
-    for (int i = 0; i < CHUNK; ++i) {
-        if (i < n) {
-            const size_t row = (size_t)(t0 + i) * 3 * p.W;
-            z[i] = column<TI>(p, row + c) + bz;
-            u[i] = column<TI>(p, row + p.W + c) + bu;
+        for (int i = 0; i < CHUNK; ++i) {
+            const size_t row = (size_t)(t0 + min(i, n - 1)) * 3 * p.W;
+            z[i] = to_float(src[row + c]);
+            u[i] = to_float(src[row + p.W + c]);
+        }
+#pragma unroll
+        for (int i = 0; i < CHUNK; ++i) {
+            z[i] += bz;
+            u[i] += bu;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < CHUNK; ++i) {
+            if (i < n) {
+                const size_t row = (size_t)(t0 + i) * 3 * p.W;
+                z[i] = column<TI>(p, row + c) + bz;
+                u[i] = column<TI>(p, row + p.W + c) + bu;
+            }
         }
     }
     float P = 1.f, R = 0.f;
@@ -96,37 +113,65 @@ __global__ void __launch_bounds__(NT, 8) mingru_pairs_kernel(const ScanParams p)
     pr[p.W + c] = R;
 }
 
-// a thread per (request, column): the state every chunk starts from, and the state the portion leaves
-__global__ void __launch_bounds__(NT) mingru_starts_kernel(const ScanParams p) {
+// The state every chunk starts from, and the state the portion leaves.  A CTA per (request, 32 columns): its
+// eight warps each take an eighth of the chunks, fold their pairs into one, learn their own start from the
+// warps before them, and walk their chunks again.  A lane is a column, so rows are read side by side.
+constexpr int SW = 8;         // warps of the starts kernel
+__global__ void __launch_bounds__(32 * SW) mingru_starts_kernel(const ScanParams p) {
+    __shared__ float sP[SW][32], sR[SW][32];
     grid_launch_dependents();
     grid_dependency_wait();
-    const int c = blockIdx.x * NT + threadIdx.x, b = blockIdx.z;
-    if (c >= p.W) return;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int c = blockIdx.x * 32 + lane, b = blockIdx.z;
+    const bool live = c < p.W;
+    const int cc = live ? c : p.W - 1;
     const int len = p.q_start[b + 1] - p.q_start[b];
     const int chunks = (len + CHUNK - 1) / CHUNK;
-    float* st = p.state + (size_t)p.state_slot[b] * p.W + c;
+    const int per = (chunks + SW - 1) / SW;
+    const int j0 = min(warp * per, chunks), j1 = min(j0 + per, chunks);
+    const float* pr = p.pairs + (size_t)b * p.n_chunks * 2 * p.W + cc;
+    float P = 1.f, R = 0.f;
+    for (int j = j0; j < j1; j += 8) {
+        float Pj[8], Rj[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const size_t at = (size_t)min(j + i, j1 - 1) * 2 * p.W;
+            Pj[i] = pr[at];
+            Rj[i] = pr[at + p.W];
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            if (j + i < j1) {
+                R = fmaf(Pj[i], R, Rj[i]);
+                P *= Pj[i];
+            }
+        }
+    }
+    sP[warp][lane] = P;
+    sR[warp][lane] = R;
+    __syncthreads();
+    float* st = p.state + (size_t)p.state_slot[b] * p.W + cc;
     float S = p.fresh[b] ? 0.f : *st;
-    const float* pr = p.pairs + (size_t)b * p.n_chunks * 2 * p.W + c;
-    float* out = p.starts + (size_t)b * p.n_chunks * p.W + c;
-    int j = 0;
-    for (; j + 8 <= chunks; j += 8) {
-        float P[8], R[8];
+    for (int w = 0; w < warp; ++w) S = fmaf(sP[w][lane], S, sR[w][lane]);
+    float* out = p.starts + (size_t)b * p.n_chunks * p.W + cc;
+    for (int j = j0; j < j1; j += 8) {
+        float Pj[8], Rj[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-            P[i] = pr[(size_t)(j + i) * 2 * p.W];
-            R[i] = pr[(size_t)(j + i) * 2 * p.W + p.W];
+            const size_t at = (size_t)min(j + i, j1 - 1) * 2 * p.W;
+            Pj[i] = pr[at];
+            Rj[i] = pr[at + p.W];
         }
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-            out[(size_t)(j + i) * p.W] = S;
-            S = fmaf(P[i], S, R[i]);
+            if (j + i < j1) {
+                if (live) out[(size_t)(j + i) * p.W] = S;
+                S = fmaf(Pj[i], S, Rj[i]);
+            }
         }
     }
-    for (; j < chunks; ++j) {
-        out[(size_t)j * p.W] = S;
-        S = fmaf(pr[(size_t)j * 2 * p.W], S, pr[(size_t)j * 2 * p.W + p.W]);
-    }
-    if (chunks > 0) *st = S;
+    __syncthreads();                                       // every warp has read the state it started from
+    if (live && j0 < j1 && j1 == chunks) *st = S;          // the warp that owns the last chunk leaves the state
 }
 
 template <typename TI, typename TO, bool FAST>
@@ -140,13 +185,30 @@ __global__ void __launch_bounds__(NT, 8) mingru_scan_kernel(const ScanParams p) 
     if (n <= 0) return;
     const float bz = p.bias ? p.bias[c] : 0.f, bu = p.bias ? p.bias[p.W + c] : 0.f, bg = p.bias ? p.bias[2 * p.W + c] : 0.f;
     float z[CHUNK], u[CHUNK], g[CHUNK];
+    if (p.splits == 1 && n > 1) {
+        const TI* src = reinterpret_cast<const TI*>(p.proj);      // (as in the kernel above)
 #pragma unroll
-    for (int i = 0; i < CHUNK; ++i) {
-        if (i < n) {
-            const size_t row = (size_t)(t0 + i) * 3 * p.W;
-            z[i] = column<TI>(p, row + c) + bz;
-            u[i] = column<TI>(p, row + p.W + c) + bu;
-            g[i] = column<TI>(p, row + 2 * p.W + c) + bg;
+        for (int i = 0; i < CHUNK; ++i) {
+            const size_t row = (size_t)(t0 + min(i, n - 1)) * 3 * p.W;
+            z[i] = to_float(src[row + c]);
+            u[i] = to_float(src[row + p.W + c]);
+            g[i] = to_float(src[row + 2 * p.W + c]);
+        }
+#pragma unroll
+        for (int i = 0; i < CHUNK; ++i) {
+            z[i] += bz;
+            u[i] += bu;
+            g[i] += bg;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < CHUNK; ++i) {
+            if (i < n) {
+                const size_t row = (size_t)(t0 + i) * 3 * p.W;
+                z[i] = column<TI>(p, row + c) + bz;
+                u[i] = column<TI>(p, row + p.W + c) + bu;
+                g[i] = column<TI>(p, row + 2 * p.W + c) + bg;
+            }
         }
     }
     float* st = p.state + (size_t)p.state_slot[b] * p.W + c;
@@ -195,7 +257,7 @@ extern "C" int tl_mingru_scan(const void* proj, int in_dtype, int splits, long l
     do {                                                                                         \
         if (p.n_chunks > 1) {                                                                    \
             e = tl_launch(mingru_pairs_kernel<TI, FAST>, grid, block, 0, s, p);                  \
-            if (e == cudaSuccess) e = tl_launch(mingru_starts_kernel, dim3(grid.x, 1, n_seqs), block, 0, s, p); \
+            if (e == cudaSuccess) e = tl_launch(mingru_starts_kernel, dim3((width + 31) / 32, 1, n_seqs), dim3(32 * SW), 0, s, p); \
         }                                                                                        \
         if (e == cudaSuccess) e = tl_launch(mingru_scan_kernel<TI, TO, FAST>, grid, block, 0, s, p); \
     } while (0)

@@ -693,6 +693,7 @@ class NativeOps:
               "experts: x [T, dim], chosen and weights [T, top]")
         T, dim = x.shape
         top = chosen.shape[1]
+        _need(top <= 64, f"a token may use at most 64 experts, got {top}")
         E, hidden = w_up.shape[0], w_up.shape[1]
         _need(w_up.shape == (E, hidden, dim) and w_down.dim() == 2 and w_down.shape[0] == dim and w_down.shape[1] >= E * hidden,
               "experts: w_up [E, hidden, dim], w_down [dim, >= E * hidden]")
