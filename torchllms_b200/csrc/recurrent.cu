@@ -10,7 +10,7 @@
 //
 // A request's portion is a linear recurrence S_t = p_t S_(t-1) + r_t, so it can be cut into chunks:
 // every chunk first reduces to the pair (P, R) with S_end = P S_start + R (kernel 1, all chunks side
-// by side), then a thread per column walks the chunks' pairs in order and leaves every chunk's
+// by side), then the chunks' pairs are walked in order, in two levels, which leaves every chunk's
 // S_start and the request's new state (kernel 2), then every chunk runs its tokens again from its
 // S_start, writing the outputs (kernel 3).  Portions no longer than one chunk (decode steps among
 // them) run as kernel 3 alone.  A thread owns one column of one chunk and fetches the chunk's
