@@ -305,6 +305,11 @@ def test_small_kernels_against_the_plain_functions(backend):
         hist = levels.clone().to(dev)
         ops.depth_mix(hist, coef.to(dev), 4, hist[4])
         torch.testing.assert_close(hist[4].cpu(), (levels[:4].double() * coef.double()[:, None, None]).sum(0).float(), atol=2e-5, rtol=1e-5)
+        hist = levels.clone().to(dev)                   # ... and with the next layer's input norm from the same kernel
+        rows = ops.depth_mix(hist, coef.to(dev), 4, hist[4], then_weight=w2.to(dev), then_eps=1e-5, out_dtype=dtype)
+        mixed = (levels[:4].double() * coef.double()[:, None, None]).sum(0)
+        torch.testing.assert_close(hist[4].cpu(), mixed.float(), atol=2e-5, rtol=1e-5)
+        torch.testing.assert_close(rows.float().cpu(), plain.scalar_norm(mixed, torch.tensor(1.3), 1e-5).float(), **tol)
         # rotation of a part of every head, keys and values into pages of their own shapes
         nq, nk, nv, hd, vd, rot, page = 4, 2, 1, 12, 20, 8, 4
         proj = rnd(T, (nq + nk) * hd + nv * vd + 3).to(dtype)

@@ -77,10 +77,13 @@ class TorchOps:
             return (h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + then_eps) * then_weight).to(out_dtype)
         return self.stream_rows(h, out_dtype)
 
-    def depth_mix(self, history, coef, n, out):
-        """out = sum_j coef[j] * history[j] over the first n levels (float32)."""
+    def depth_mix(self, history, coef, n, out, then_weight=None, then_eps=0.0, out_dtype=None):
+        """out = sum_j coef[j] * history[j] over the first n levels (float32); with then_weight also the
+        RMS norm of out under it, in out_dtype."""
         out.copy_((history[:n] * coef[:n, None, None]).sum(0))
-        return out
+        if then_weight is None:
+            return None
+        return (out * torch.rsqrt(out.pow(2).mean(-1, keepdim=True) + then_eps) * then_weight).to(out_dtype)
 
     @staticmethod
     def _act(x, kind):

@@ -606,6 +606,29 @@ __global__ void depth_mix_kernel(const float* __restrict__ levels, long long lev
     }
 }
 
+// The same average, a row per CTA, with the RMS norm of the result under weight / eps beside it (the input norm of
+// the layer that reads the average next): the row stays in shared memory between the two passes.
+template <typename TO>
+__global__ void depth_mix_norm_kernel(const float* __restrict__ levels, long long level_stride, const float* __restrict__ coef,
+                                      int n, float* __restrict__ out, const float* __restrict__ weight, TO* __restrict__ normed,
+                                      int dim, float eps) {
+    extern __shared__ __align__(16) float row_buf[];
+    __shared__ float part[33];
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const size_t base = (size_t)blockIdx.x * dim;
+    float ssq = 0.f;
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+        float acc = 0.f;
+        for (int j = 0; j < n; ++j) acc = fmaf(__ldg(coef + j), levels[j * level_stride + base + d], acc);
+        out[base + d] = acc;
+        row_buf[d] = acc;
+        ssq = fmaf(acc, acc, ssq);
+    }
+    const float r = rsqrtf(block_sum(ssq, part) / (float)dim + eps);
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) normed[base + d] = from_float<TO>(row_buf[d] * r * weight[d]);
+}
+
 // in: [splits][n_tokens][(gated ? 2 : 1) * hidden]; out: [n_tokens][hidden]
 template <typename TI, typename TO>
 __global__ void act_kernel(const TI* __restrict__ in, int splits, long long plane, TO* __restrict__ out,
@@ -722,6 +745,25 @@ extern "C" int tl_depth_mix(const float* levels, long long level_stride, const f
                                    level_stride, coef, n, out, count);
     return (int)tl_launch(depth_mix_kernel<false>, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, levels,
                           level_stride, coef, n, out, count);
+}
+
+// As tl_depth_mix for rows of `dim` elements ([n_rows][dim] per level), and normed = out / sqrt(mean(out^2) + eps) * weight
+// in out_dtype.
+extern "C" int tl_depth_mix_norm(const float* levels, long long level_stride, const float* coef, int n, float* out,
+                                 const float* weight, void* normed, int out_dtype, int n_rows, int dim, float eps, void* stream) {
+    if (n_rows <= 0) return TL_OK;
+    if (n < 1 || dim <= 0) return TL_BAD_SIZE;
+    const size_t smem = (size_t)dim * sizeof(float);
+    if (smem > 48 * 1024) return TL_TOO_LARGE;
+    const dim3 grid(n_rows), block(row_threads(dim));
+    cudaStream_t s = (cudaStream_t)stream;
+    if (out_dtype == TL_F32)
+        return (int)tl_launch(depth_mix_norm_kernel<float>, grid, block, smem, s, levels, level_stride, coef, n, out, weight,
+                              (float*)normed, dim, eps);
+    if (out_dtype == TL_BF16)
+        return (int)tl_launch(depth_mix_norm_kernel<__nv_bfloat16>, grid, block, smem, s, levels, level_stride, coef, n, out, weight,
+                              (__nv_bfloat16*)normed, dim, eps);
+    return TL_BAD_DTYPE;
 }
 
 // gated: in is [splits][n_tokens][2 * hidden] (gate columns first) and out = act(gate) * up; else in is

@@ -117,7 +117,9 @@ class Model:
         else:
             residual = Residual(self.ops.embed(ctx.token_ids, self.embedding, scale=self.spec.embedding_scale,
                                                positions=ctx.positions, position_table=self.position_table))
-        for i, run in enumerate(self.spec.run_order):
+        order = self.spec.run_order
+        for i, run in enumerate(order):
+            residual.next_norm = self.blocks[order[i + 1].layer].input_norm if i + 1 < len(order) else None
             self.blocks[run.layer].forward(residual, ctx, views[i])
             if residual.history is not None and residual.level != i + 1:
                 self._next_level(residual)      # a block that reads no earlier results: the stream passes as it is

@@ -451,19 +451,36 @@ class NativeOps:
     _ACTS = {"silu": 0, "gelu_tanh": 1, "relu2": 2}
 
     @_timed
-    def depth_mix(self, history: torch.Tensor, coef: torch.Tensor, n: int, out: torch.Tensor) -> torch.Tensor:
+    def depth_mix(self, history: torch.Tensor, coef: torch.Tensor, n: int, out: torch.Tensor,
+                  then_weight: Optional[torch.Tensor] = None, then_eps: float = 0.0,
+                  out_dtype: Optional[torch.dtype] = None) -> Optional[torch.Tensor]:
         """``out = sum_j coef[j] * history[j]`` over the first ``n`` levels of ``history``
-        (float32 ``[levels, T, dim]``); ``out`` (``[T, dim]``) may be a later level of it."""
+        (float32 ``[levels, T, dim]``); ``out`` (``[T, dim]``) may be a later level of it.  With
+        ``then_weight`` the same kernel also returns the RMS norm of ``out`` under that weight and
+        ``then_eps`` in ``out_dtype`` (the input norm of whoever reads the average next)."""
         _cuda_contig(history, "history", torch.float32)
         _cuda_contig(coef, "depth coefficients", torch.float32)
         _cuda_contig(out, "depth_mix output", torch.float32)
         _need(history.dim() == 3 and 1 <= n <= history.shape[0] and coef.numel() >= n and out.shape == history.shape[1:],
               "depth_mix: history [levels, T, dim], n coefficients, out [T, dim]")
+        T, dim = out.shape
+        if then_weight is not None and dim * 4 <= 48 * 1024:
+            _cuda_contig(then_weight, "following norm's weight", torch.float32)
+            _need(then_weight.numel() == dim and out_dtype in _DT, "the following norm's weight must match the stream's width")
+            normed = torch.empty((T, dim), dtype=out_dtype, device=out.device)
+            rc = self._lib("sublayer").tl_depth_mix_norm(_ptr(history), ctypes.c_longlong(history.stride(0)), _ptr(coef), int(n),
+                                                        _ptr(out), _ptr(then_weight), _ptr(normed), _DT[out_dtype], T, dim,
+                                                        ctypes.c_float(then_eps), _stream())
+            _check(rc, "depth_mix_norm")
+            self.launches += 1
+            return normed
         rc = self._lib("sublayer").tl_depth_mix(_ptr(history), ctypes.c_longlong(history.stride(0)), _ptr(coef), int(n), _ptr(out),
                                                ctypes.c_longlong(out.numel()), _stream())
         _check(rc, "depth_mix")
         self.launches += 1
-        return out
+        if then_weight is not None:
+            return self.rmsnorm(out, None, then_weight, then_eps, out_dtype=out_dtype)
+        return None
 
     def _act(self, x: torch.Tensor, kind: str, out_dtype: Optional[torch.dtype], gated: bool) -> torch.Tensor:
         _need(kind in self._ACTS, f"unknown activation {kind!r}; known: {', '.join(self._ACTS)}")

@@ -220,6 +220,9 @@ class Block(Part):
     def state_need(self) -> Optional[StateNeed]:
         return None
 
+    # the norm that this block applies to the stream before anything else, if it has one (``Residual.next_norm``)
+    input_norm: Optional[Norm] = None
+
 
 class Residual:
     """The residual stream ``h`` (float32, ``[T, dim]``) and a delta not yet added.
@@ -239,9 +242,14 @@ class Residual:
     (``ModelSpec.keeps_history``): ``[levels, T, dim]`` float32, level 0 the embedding output,
     level ``j`` the result of the ``j``-th layer run; ``level`` counts the finished ones, and ``h``
     is then a view of ``history[level + 1]``, the level being written.
+
+    ``next_norm`` is the norm that the next block will apply to the stream first, where the model
+    knows it (``Block.input_norm``); a block that ends in a kernel which could take that norm
+    along may do so and leave ``normed = (that norm, its rows)``, which the next block takes
+    instead of running its norm.
     """
 
-    __slots__ = ("h", "delta", "rows", "history", "level")
+    __slots__ = ("h", "delta", "rows", "history", "level", "next_norm", "normed")
 
     def __init__(self, h: torch.Tensor, delta: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None,
                  history: Optional[torch.Tensor] = None):
@@ -250,6 +258,8 @@ class Residual:
         self.rows = rows
         self.history = history
         self.level = 0
+        self.next_norm = None
+        self.normed = None
 
 
 # --------------------------------------------------------------------------- registries

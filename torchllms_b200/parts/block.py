@@ -15,6 +15,7 @@ import torch
 
 from ..weights.loader import ExpectedTensor
 from .base import FEED_FORWARDS, MIXERS, NORMS, Block, BuildEnv, Residual, register_block
+from .norm import RMSNorm
 from .spec import PartSpec
 
 
@@ -142,6 +143,7 @@ class SandwichBlock(Block):
         self.env = env
         self.mixer = MIXERS.build(mixer, env)
         self.mixer_norm = NORMS.build(mixer_norm, env)
+        self.input_norm = self.mixer_norm
         self.mixer_out_norm = NORMS.build(mixer_out_norm, env)
         self._subparts = [(mixer_prefix, self.mixer), (mixer_norm_prefix, self.mixer_norm),
                           (mixer_out_norm_prefix, self.mixer_out_norm)]
@@ -186,7 +188,12 @@ class SandwichBlock(Block):
     def forward(self, residual: Residual, ctx, cache) -> None:
         if residual.delta is not None:
             raise RuntimeError("a sandwich block cannot follow a block that leaves its sum pending")
-        y = self.mixer.forward(self.mixer_norm.forward(residual), ctx, cache)
+        if residual.normed is not None and residual.normed[0] is self.mixer_norm:
+            x = residual.normed[1]                       # the block before took this norm along with its last kernel
+        else:
+            x = self.mixer_norm.forward(residual)
+        residual.normed = None
+        y = self.mixer.forward(x, ctx, cache)
         if self.feed_forward is None:
             self.mixer_out_norm.fold_normed(residual, y, want_rows=False)
         else:
@@ -198,5 +205,12 @@ class SandwichBlock(Block):
                 raise RuntimeError(f"this layer averages over {self.depth_inputs} levels of the model's history, "
                                    f"but {'there is none' if history is None else f'{level + 2} exist'}")
             nxt = history[level + 2]
-            self.env.ops.depth_mix(history, self.depth_coef, self.depth_inputs, nxt)
+            follow = residual.next_norm
+            if isinstance(follow, RMSNorm):
+                # the average and the next layer's input norm of it in one kernel
+                rows = self.env.ops.depth_mix(history, self.depth_coef, self.depth_inputs, nxt, then_weight=follow.weight,
+                                              then_eps=follow.eps, out_dtype=self.env.dtype)
+                residual.normed = (follow, rows)
+            else:
+                self.env.ops.depth_mix(history, self.depth_coef, self.depth_inputs, nxt)
             residual.h, residual.rows, residual.level = nxt, None, level + 1
