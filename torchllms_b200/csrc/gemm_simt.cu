@@ -16,8 +16,8 @@ namespace {
 
 constexpr int BM = 64, BN = 64, BK = 16, PAD = 4, NT = 256;
 
-template <typename T, typename TO, typename TA = T>
-__global__ void __launch_bounds__(NT) gemm_simt_kernel(const TA* __restrict__ A, const T* __restrict__ W,
+template <typename T, typename TO>
+__global__ void __launch_bounds__(NT) gemm_simt_kernel(const T* __restrict__ A, const T* __restrict__ W,
                                                        TO* __restrict__ C, int M, int N, int K,
                                                        long long lda, long long ldc, long long a_batch,
                                                        long long w_batch, long long c_batch) {
@@ -73,12 +73,12 @@ __global__ void __launch_bounds__(NT) gemm_simt_kernel(const TA* __restrict__ A,
     }
 }
 
-template <typename T, typename TO, typename TA = T>
+template <typename T, typename TO>
 int launch(const void* A, const void* W, void* C, int M, int N, int K, cudaStream_t s, int batches = 1,
            long long lda = -1, long long ldc = -1, long long a_batch = 0, long long w_batch = 0, long long c_batch = 0) {
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, batches);
     if (grid.y > 65535 || batches > 65535) return TL_BAD_SIZE;
-    gemm_simt_kernel<T, TO, TA><<<grid, NT, 0, s>>>((const TA*)A, (const T*)W, (TO*)C, M, N, K, lda < 0 ? K : lda,
+    gemm_simt_kernel<T, TO><<<grid, NT, 0, s>>>((const T*)A, (const T*)W, (TO*)C, M, N, K, lda < 0 ? K : lda,
                                                 ldc < 0 ? N : ldc, a_batch, w_batch, c_batch);
     TL_LAUNCH_CHECK();
     return TL_OK;
@@ -95,13 +95,6 @@ extern "C" int tl_gemm_simt(const void* A, const void* W, void* C, int in_dtype,
     if (in_dtype == TL_BF16 && out_dtype == TL_BF16) return launch<__nv_bfloat16, __nv_bfloat16>(A, W, C, M, N, K, s);
     if (in_dtype == TL_BF16 && out_dtype == TL_F32) return launch<__nv_bfloat16, float>(A, W, C, M, N, K, s);
     return TL_BAD_DTYPE;
-}
-
-// bfloat16 rows against a float32 matrix, float32 out (a router's logits: 32-bit arithmetic on the rounded stream)
-extern "C" int tl_gemm_simt_rows_bf16(const void* A, const void* W, void* C, int M, int N, int K, void* stream) {
-    if (M <= 0 || N <= 0) return TL_OK;
-    if (K <= 0) return TL_BAD_SIZE;
-    return launch<float, float, __nv_bfloat16>(A, W, C, M, N, K, (cudaStream_t)stream);
 }
 
 namespace {

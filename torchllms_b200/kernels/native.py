@@ -670,10 +670,7 @@ class NativeOps:
             logits = self.gemm_simt(x, w_router, torch.float32)
         elif torch.backends.cuda.matmul.allow_tf32:
             # many tokens, and the library's float32 product would not be one: this library's own
-            logits = torch.empty((T, rows), dtype=torch.float32, device=x.device)
-            _check(self._lib("gemm_simt").tl_gemm_simt_rows_bf16(_ptr(x), _ptr(w_router), _ptr(logits), T, rows, dim, _stream()),
-                   "gemm_simt (router)")
-            self.launches += 1
+            logits = self.gemm_simt(x.float(), w_router, torch.float32)
         else:
             # many tokens: the library's float32 product of the rows as the rounded stream holds them (true
             # 32-bit arithmetic: the reduced-precision matrix mode is off), as linear() takes the library for so many rows
